@@ -6,7 +6,7 @@ launches nothing (the reference keeps the same split, src/block_pool.h:14-15).  
 are made by ``make_storage`` and handed to the parts as views.
 
 Groups.  Every cache entry of the run order states a need (``PagedKVNeed`` / ``StateNeed`` / none).
-Paged entries with the same (kv heads, head size, window) form a *group*: the group has one page
+Paged entries with the same (kv heads, key and value size, window) form a *group*: the group has one page
 pool and one block table per request, and a page id addresses the same page in every entry of the
 group (the reference has one implicit group: one block id spans all layers,
 kernels/batch_gpu.cu:75,114-118).  Groups with a window give pages back as soon as every later
@@ -88,7 +88,7 @@ class CacheGroup:
     pool: PagePool
     page_size: int
     k: Optional[torch.Tensor] = None     # [len(cache_ids), n_pages, kv_heads, page_size, head_dim]
-    v: Optional[torch.Tensor] = None     # the same with the need's value size last
+    v: Optional[torch.Tensor] = None     # the same with the need's value size last (None: values lie in the key rows)
 
     @property
     def window(self) -> Optional[int]:
@@ -109,7 +109,7 @@ class PagedKVView:
     """What an attention part gets for one cache entry."""
     group: int
     k: torch.Tensor          # [n_pages, kv_heads, page_size, head_dim]
-    v: torch.Tensor
+    v: Optional[torch.Tensor]  # None where the values are the first channels of the key rows
     page_size: int
     window: Optional[int]
 
@@ -130,7 +130,7 @@ class CacheManager:
         def place(key, need):
             """key: the cache index, or (cache index, name, ...) for a leaf of a composite need."""
             if isinstance(need, PagedKVNeed):
-                gkey = (need.num_kv_heads, need.head_dim, need.value_dim, need.window)
+                gkey = (need.num_kv_heads, need.head_dim, need.value_dim, need.window, need.values_in_keys)
                 g = by_key.get(gkey)
                 if g is None:
                     g = CacheGroup(len(self.groups), need, [], PagePool(n_pages), page_size)
@@ -158,7 +158,7 @@ class CacheManager:
         for g in self.groups:
             shape = (len(g.cache_ids), g.pool.n_pages, g.need.num_kv_heads, self.page_size)
             g.k = torch.zeros(shape + (g.need.head_dim,), dtype=dtype, device=device)
-            g.v = torch.zeros(shape + (g.need.value_dim,), dtype=dtype, device=device)
+            g.v = None if g.need.values_in_keys else torch.zeros(shape + (g.need.value_dim,), dtype=dtype, device=device)
         for cid, need in self.state_needs.items():
             # a state tensor declared with dtype None takes the storage's (the compute dtype of the model)
             self.state[cid] = {name: torch.zeros((self.n_slots,) + tuple(shape), dtype=dt or dtype, device=device)
@@ -167,7 +167,7 @@ class CacheManager:
     def storage_bytes(self, dtype: torch.dtype) -> int:
         item = torch.empty((), dtype=dtype).element_size()
         return sum(len(g.cache_ids) * g.pool.n_pages * g.need.num_kv_heads * self.page_size *
-                   (g.need.head_dim + g.need.value_dim) * item for g in self.groups)
+                   (g.need.head_dim + g.need.stored_value_dim) * item for g in self.groups)
 
     def view(self, cache_id: int):
         """PagedKVView, the dict of state tensors, a dict of such views by name for a composite need, or None."""
@@ -182,7 +182,7 @@ class CacheManager:
             g = self.groups[gi]
             if g.k is None:
                 raise CacheError("make_storage() has not been called")
-            return PagedKVView(gi, g.k[li], g.v[li], self.page_size, g.window)
+            return PagedKVView(gi, g.k[li], g.v[li] if g.v is not None else None, self.page_size, g.window)
         if key in self.state_needs:
             return self.state[key]
         return None

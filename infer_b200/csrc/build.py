@@ -31,6 +31,7 @@ MODULES: Dict[str, str] = {
     "plain": "plain_ops.cu",
     "seq": "seq_ops.cu",         # filters over time, pair rotation, gated recurrence, side-by-side sublayers
     "mix": "mix_ops.cu",         # norms on sublayer results, decayed and delta-rule recurrences, routers, row norms of q and k
+    "latent": "latent_ops.cu",   # attention through low-rank latents, layer norm, sigmoid router, capped logits
     "gemvb": "gemv_bulk.cu",
     "gemm": "gemm_tcgen05.cu",
     "attn": "attention_fast.cu",

@@ -1,0 +1,762 @@
+// Kernels for attention through low-rank latents, and the small pieces of the designs that use it.
+//
+// A position leaves ONE row behind for all heads: [c | r], c the normalised low-rank row (kv_rank channels) from
+// which every head's keys and values are up-projections, r a small rotated key part that all heads share. The pages
+// hold these rows and nothing else. Attention runs in the latent space: a head's query is carried through its key
+// up-projection once (q_lat = [W_uk_h^T q_plain | rotate(q_rot)]), so that score = q_lat . [c | r], the context is
+// the weighted sum of the c rows, and the head's value up-projection is applied to that sum:
+//
+//   layer_norm        (x - mean) / sqrt(var + eps) * w per row, float in, compute dtype out, optional row gather
+//   latent_prepare    per token: rmsnorm of the query latent -> cq; rmsnorm of the kv latent and the rotation of the
+//                     shared key part -> the token's row in its page
+//   latent_query      per (token, head): q_lat from the up-projected query
+//   latent_attention  paged attention of H query heads over the one row per position; values are the first kv_rank
+//                     channels of the key row; window optional; keys in chunks of 128 aligned to absolute positions,
+//                     chunk results merged in ascending order (in the CTA, or by latent_attention_merge when a
+//                     decode step spreads a token's chunks over CTAs; the arithmetic is the same, so the bits are)
+//   latent_output     per (token, head): W_uv_h applied to the latent context, times sigmoid(gate) and a constant
+//   route_sigmoid     router with sigmoid scores, a correction that only the choice sees, weights not renormalised
+//   scaled_relu_sq    hidden layer of ungated experts: relu(x)^2 times the token's weight for the expert
+//   scale_softcap     logits <- cap * tanh(logits * scale / cap), in place
+//
+// Storage float or bfloat16, arithmetic float. Every sum is taken in an order that depends on sizes and absolute
+// positions only, never on the batch.
+#include "common.cuh"
+
+IB_DEFINE_LAST_ERROR()
+
+#define IB_LAUNCH(kernel, grid, block, smem, ...)                                                              \
+    do {                                                                                                       \
+        const int rc_ = ib::launch(#kernel, kernel, dim3(grid), dim3(block), size_t(smem), stream, 1u, __VA_ARGS__); \
+        if (rc_) return rc_;                                                                                   \
+    } while (0)
+
+namespace {
+
+using bf16 = __nv_bfloat16;
+
+inline unsigned blocks_for(int64_t n, int threads) { return unsigned((n + threads - 1) / threads); }
+
+__device__ __forceinline__ float sigmoid_(float x) { return 1.0f / (1.0f + expf(-x)); }
+
+// ------------------------------------------------------------------------------------------------
+// Layer norm with a weight and no bias. One CTA per output row; the row waits in shared memory between the passes
+// (mean, mean of squared deviations, result).
+constexpr int LN_THREADS = 256;
+
+template <typename TOut>
+__global__ void __launch_bounds__(LN_THREADS)
+layer_norm_kernel(const float* __restrict__ x, const float* __restrict__ w, float eps, int64_t hidden,
+                  const int* __restrict__ rows, TOut* __restrict__ out) {
+    ib::pdl_wait();
+    extern __shared__ float ln_row[];
+    __shared__ float red[32];
+    const int64_t r = blockIdx.x;
+    const float* src = x + (rows ? int64_t(rows[r]) : r) * hidden;
+    float s = 0.0f;
+    for (int64_t i = threadIdx.x; i < hidden; i += LN_THREADS) {
+        const float v = src[i];
+        ln_row[i] = v;
+        s += v;
+    }
+    const float mean = ib::block_sum(s, red) / float(hidden);
+    float q = 0.0f;
+    for (int64_t i = threadIdx.x; i < hidden; i += LN_THREADS) {
+        const float d = ln_row[i] - mean;
+        q = fmaf(d, d, q);
+    }
+    const float inv = 1.0f / sqrtf(ib::block_sum(q, red) / float(hidden) + eps);
+    for (int64_t i = threadIdx.x; i < hidden; i += LN_THREADS)
+        out[r * hidden + i] = ib::from_f32<TOut>((ln_row[i] - mean) * inv * w[i]);
+}
+
+// ------------------------------------------------------------------------------------------------
+// The two latents of a token, from the float rows of the down-projections [.. | query latent | .. | kv latent, shared
+// key part | ..]. Query latent: divided by its root mean square, times wq -> cq. Kv latent likewise with wkv -> the
+// first kv_rank channels of the token's row in its page; the shared key part is rotated by the token's position
+// (tables [positions][n_rot / 2]; layout 0: channel 2i turns with 2i + 1, layout 1: channel i with i + n_rot / 2;
+// channels from n_rot on pass) and follows. Either half may be absent (q_rank 0; write 0).
+constexpr int LP_THREADS = 128;
+
+template <typename T>
+__global__ void __launch_bounds__(LP_THREADS)
+latent_prepare_kernel(const float* __restrict__ rows, int64_t ld, int q_col, int q_rank, int kv_col, int kv_rank, int rot_dim,
+                      const float* __restrict__ wq, const float* __restrict__ wkv, float eps, const float* __restrict__ cos_t,
+                      const float* __restrict__ sin_t, int layout, int n_rot, const int* __restrict__ positions,
+                      const int* __restrict__ token_seg, const int* __restrict__ block_table, int64_t max_blocks,
+                      T* __restrict__ cq, T* __restrict__ cache, int page_size, int64_t n_pages, int write, int* status) {
+    ib::pdl_wait();
+    __shared__ float red[32];
+    const int64_t t = blockIdx.x;
+    const int tid = threadIdx.x;
+    const float* src = rows + t * ld;
+    if (q_rank > 0) {
+        float s = 0.0f;
+        for (int i = tid; i < q_rank; i += LP_THREADS) {
+            const float v = src[q_col + i];
+            s = fmaf(v, v, s);
+        }
+        const float inv = 1.0f / sqrtf(ib::block_sum(s, red) / float(q_rank) + eps);
+        for (int i = tid; i < q_rank; i += LP_THREADS) cq[t * q_rank + i] = ib::from_f32<T>(src[q_col + i] * inv * wq[i]);
+    }
+    if (!write) return;
+    float s = 0.0f;
+    for (int i = tid; i < kv_rank; i += LP_THREADS) {
+        const float v = src[kv_col + i];
+        s = fmaf(v, v, s);
+    }
+    const float inv = 1.0f / sqrtf(ib::block_sum(s, red) / float(kv_rank) + eps);
+    const int pos = positions[t];
+    const int page = block_table[int64_t(token_seg[t]) * max_blocks + pos / page_size];
+    if (page < 0 || page >= n_pages) {
+        if (status && tid == 0) atomicExch(status, 2);
+        return;
+    }
+    T* dst = cache + (int64_t(page) * page_size + pos % page_size) * (kv_rank + rot_dim);
+    for (int i = tid; i < kv_rank; i += LP_THREADS) dst[i] = ib::from_f32<T>(src[kv_col + i] * inv * wkv[i]);
+    const float* r = src + kv_col + kv_rank;
+    T* rd = dst + kv_rank;
+    const int half = n_rot / 2;
+    for (int i = tid; i < half; i += LP_THREADS) {
+        const int a = layout == 0 ? 2 * i : i, b = layout == 0 ? 2 * i + 1 : i + half;
+        const float c = cos_t[int64_t(pos) * half + i], sn = sin_t[int64_t(pos) * half + i];
+        const float u = r[a], v = r[b];
+        rd[a] = ib::from_f32<T>(u * c - v * sn);
+        rd[b] = ib::from_f32<T>(v * c + u * sn);
+    }
+    for (int i = n_rot + tid; i < rot_dim; i += LP_THREADS) rd[i] = ib::from_f32<T>(r[i]);
+}
+
+// ------------------------------------------------------------------------------------------------
+// Queries in the latent space. q [T][H][d + dr] (a head's unrotated channels, then its rotated ones); w_uk [H][d][R]
+// (the key up-projection as checkpoints store it, [H * d, R]); out [T][H][R + dr]:
+//   out[t, h, r] = sum_e q[t, h, e] * w_uk[h, e, r] (e ascending),  out[t, h, R:] = rotate(q[t, h, d:], position).
+// One CTA per (LQ_TOK tokens, head, 128 latent channels): a weight is read once for LQ_TOK tokens.
+constexpr int LQ_TOK = 8, LQ_THREADS = 128;
+
+template <typename T>
+__global__ void __launch_bounds__(LQ_THREADS)
+latent_query_kernel(const T* __restrict__ q, const T* __restrict__ w_uk, const float* __restrict__ cos_t,
+                    const float* __restrict__ sin_t, int layout, int n_rot, const int* __restrict__ positions,
+                    T* __restrict__ out, int64_t n_tokens, int n_heads, int d, int dr, int R) {
+    ib::pdl_wait();
+    extern __shared__ float lq_q[];                   // [LQ_TOK][d]
+    const int64_t t0 = int64_t(blockIdx.x) * LQ_TOK;
+    const int h = blockIdx.y, tid = threadIdx.x;
+    const int nt = int(min(int64_t(LQ_TOK), n_tokens - t0));
+    for (int i = tid; i < LQ_TOK * d; i += LQ_THREADS) {
+        const int tt = i / d, e = i - tt * d;
+        lq_q[i] = tt < nt ? ib::to_f32(q[((t0 + tt) * n_heads + h) * (d + dr) + e]) : 0.0f;
+    }
+    __syncthreads();
+    const int r = blockIdx.z * LQ_THREADS + tid;
+    if (r < R) {
+        float acc[LQ_TOK];
+#pragma unroll
+        for (int tt = 0; tt < LQ_TOK; tt++) acc[tt] = 0.0f;
+        const T* w = w_uk + int64_t(h) * d * R + r;
+#pragma unroll 4
+        for (int e = 0; e < d; e++) {
+            const float wv = ib::to_f32(w[int64_t(e) * R]);
+#pragma unroll
+            for (int tt = 0; tt < LQ_TOK; tt++) acc[tt] = fmaf(lq_q[tt * d + e], wv, acc[tt]);
+        }
+#pragma unroll
+        for (int tt = 0; tt < LQ_TOK; tt++)
+            if (tt < nt) out[((t0 + tt) * n_heads + h) * (R + dr) + r] = ib::from_f32<T>(acc[tt]);
+    }
+    if (blockIdx.z == 0) {
+        const int half = n_rot / 2;
+        for (int i = tid; i < nt * half; i += LQ_THREADS) {
+            const int tt = i / half, j = i - tt * half;
+            const int64_t t = t0 + tt;
+            const int pos = positions[t];
+            const int a = layout == 0 ? 2 * j : j, b = layout == 0 ? 2 * j + 1 : j + half;
+            const float c = cos_t[int64_t(pos) * half + j], sn = sin_t[int64_t(pos) * half + j];
+            const T* src = q + (t * n_heads + h) * (d + dr) + d;
+            T* dst = out + (t * n_heads + h) * (R + dr) + R;
+            const float u = ib::to_f32(src[a]), v = ib::to_f32(src[b]);
+            dst[a] = ib::from_f32<T>(u * c - v * sn);
+            dst[b] = ib::from_f32<T>(v * c + u * sn);
+        }
+        const int rest = dr - n_rot;
+        for (int i = tid; i < nt * rest; i += LQ_THREADS) {
+            const int tt = i / rest, j = n_rot + (i - tt * rest);
+            const int64_t t = t0 + tt;
+            out[(t * n_heads + h) * (R + dr) + R + j] = q[(t * n_heads + h) * (d + dr) + d + j];
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// Attention over the latent rows. Keys are taken in chunks of KC positions aligned to absolute multiples of KC. A
+// chunk gives, per head, its own maximum m, the sum l of exp(score - m) and the unnormalised context o; chunks are
+// merged in ascending order by merge_state / merge_value below, whoever merges.
+constexpr int KC = 128;
+constexpr int VT = 32;                 // value rows staged at a time
+constexpr int GMAX = 8;                // query heads that share a CTA's key rows
+
+__device__ __forceinline__ void merge_state(float& M, float& L, float m, float l, float& a, float& b) {
+    const float Mn = fmaxf(M, m);
+    a = M == -INFINITY ? 0.0f : expf(M - Mn);
+    b = m == -INFINITY ? 0.0f : expf(m - Mn);
+    L = fmaf(L, a, l * b);
+    M = Mn;
+}
+__device__ __forceinline__ float merge_value(float O, float a, float o, float b) { return fmaf(O, a, o * b); }
+
+template <typename T>
+__device__ __forceinline__ void load8(const T* p, float (&x)[8]);
+template <>
+__device__ __forceinline__ void load8<float>(const float* p, float (&x)[8]) {
+    const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+    x[0] = a.x; x[1] = a.y; x[2] = a.z; x[3] = a.w; x[4] = b.x; x[5] = b.y; x[6] = b.z; x[7] = b.w;
+}
+template <>
+__device__ __forceinline__ void load8<bf16>(const bf16* p, float (&x)[8]) {
+    const uint4 u = *reinterpret_cast<const uint4*>(p);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const float2 f = __bfloat1622float2(h[i]);
+        x[2 * i] = f.x;
+        x[2 * i + 1] = f.y;
+    }
+}
+
+// GB: heads of a CTA rounded up to 1, 2, 4 or 8; NC: channel passes of a thread (dv <= NC * KC).
+// n_splits 1: the CTA walks all chunks of its token and writes the context. n_splits > 1 (steps of single tokens):
+// CTA z takes chunk z of its token and leaves (m, l, o) in `parts` [token][head][split][2 + dv].
+template <typename T, int GB, int NC>
+__global__ void __launch_bounds__(KC)
+latent_attention_kernel(const T* __restrict__ q, const T* __restrict__ cache, const int* __restrict__ block_table,
+                        int64_t max_blocks, const int* __restrict__ token_seg, const int* __restrict__ positions,
+                        T* __restrict__ out, float* __restrict__ parts, int n_heads, int group, int dk, int dv, int page_size,
+                        int window, float scale, int64_t n_pages, int n_splits, int vec, int vec_v, int* status) {
+    ib::pdl_wait();
+    const int64_t t = blockIdx.x;
+    const int g = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int pos = positions[t];
+    const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+    const int c_lo = lo / KC, c_hi = pos / KC;
+    int c_first = c_lo, c_last = c_hi;
+    if (n_splits > 1) {
+        c_first = c_last = c_lo + int(blockIdx.z);
+        if (c_first > c_hi) return;
+    }
+    const int h0 = g * group, ng = min(group, n_heads - h0);
+    extern __shared__ __align__(16) float la_sm[];
+    const int dq = (dk + 3) & ~3;
+    float* qs = la_sm;                                   // [GB][dq]
+    float* sc = qs + GB * dq;                            // [GB][KC] scores, then probabilities
+    float* ml = sc + GB * KC;                            // [GB][2]
+    int64_t* rowoff = reinterpret_cast<int64_t*>(ml + 2 * GMAX);   // [KC]
+    T* vt = reinterpret_cast<T*>(rowoff + KC);           // [VT][dv]
+    for (int i = tid; i < GB * dq; i += KC) {
+        const int gq = i / dq, e = i - gq * dq;
+        qs[i] = (gq < ng && e < dk) ? ib::to_f32(q[(t * n_heads + h0 + gq) * dk + e]) : 0.0f;
+    }
+    __syncthreads();
+    const int* table = block_table + int64_t(token_seg[t]) * max_blocks;
+    float M[GB], L[GB], O[GB][NC];
+#pragma unroll
+    for (int gq = 0; gq < GB; gq++) {
+        M[gq] = -INFINITY;
+        L[gq] = 0.0f;
+#pragma unroll
+        for (int c = 0; c < NC; c++) O[gq][c] = 0.0f;
+    }
+    for (int ch = c_first; ch <= c_last; ch++) {
+        const int base = ch * KC, key = base + tid;
+        const bool valid = key >= lo && key <= pos;
+        float acc[GB];
+#pragma unroll
+        for (int gq = 0; gq < GB; gq++) acc[gq] = 0.0f;
+        bool have = false;
+        rowoff[tid] = 0;
+        if (valid) {
+            const int page = table[key / page_size];
+            if (page < 0 || page >= n_pages) {
+                if (status) atomicExch(status, 3);
+            } else {
+                have = true;
+                const int64_t row = int64_t(page) * page_size + key % page_size;
+                rowoff[tid] = row;
+                const T* kr = cache + row * dk;
+                if (vec) {
+                    for (int e0 = 0; e0 < dk; e0 += 32) {
+                        float kv[4][8];
+#pragma unroll
+                        for (int b4 = 0; b4 < 4; b4++)
+                            if (e0 + 8 * b4 < dk) load8<T>(kr + e0 + 8 * b4, kv[b4]);
+#pragma unroll
+                        for (int b4 = 0; b4 < 4; b4++) {
+                            const int e = e0 + 8 * b4;
+                            if (e < dk) {
+#pragma unroll
+                                for (int gq = 0; gq < GB; gq++) {
+                                    const float4 a = *reinterpret_cast<const float4*>(qs + gq * dq + e);
+                                    const float4 b = *reinterpret_cast<const float4*>(qs + gq * dq + e + 4);
+                                    float x = acc[gq];
+                                    x = fmaf(a.x, kv[b4][0], x); x = fmaf(a.y, kv[b4][1], x); x = fmaf(a.z, kv[b4][2], x); x = fmaf(a.w, kv[b4][3], x);
+                                    x = fmaf(b.x, kv[b4][4], x); x = fmaf(b.y, kv[b4][5], x); x = fmaf(b.z, kv[b4][6], x); x = fmaf(b.w, kv[b4][7], x);
+                                    acc[gq] = x;
+                                }
+                            }
+                        }
+                    }
+                } else {
+                    for (int e = 0; e < dk; e++) {
+                        const float kv = ib::to_f32(kr[e]);
+#pragma unroll
+                        for (int gq = 0; gq < GB; gq++) acc[gq] = fmaf(qs[gq * dq + e], kv, acc[gq]);
+                    }
+                }
+            }
+        }
+#pragma unroll
+        for (int gq = 0; gq < GB; gq++) sc[gq * KC + tid] = have ? acc[gq] * scale : -INFINITY;
+        __syncthreads();
+        for (int gq = warp; gq < GB; gq += KC / 32) {
+            float* row = sc + gq * KC;
+            float m = -INFINITY;
+            for (int j = lane; j < KC; j += 32) m = fmaxf(m, row[j]);
+            m = ib::warp_max(m);
+            float l = 0.0f;
+            for (int j = lane; j < KC; j += 32) {
+                const float pv = row[j] > -INFINITY ? expf(row[j] - m) : 0.0f;
+                row[j] = pv;
+                l += pv;
+            }
+            l = ib::warp_sum(l);
+            if (lane == 0) { ml[2 * gq] = m; ml[2 * gq + 1] = l; }
+        }
+        __syncthreads();
+        const int j0 = max(lo, base) - base, j1 = min(pos, base + KC - 1) - base;
+        float o[GB][NC];
+#pragma unroll
+        for (int gq = 0; gq < GB; gq++)
+#pragma unroll
+            for (int c = 0; c < NC; c++) o[gq][c] = 0.0f;
+        for (int js = j0; js <= j1; js += VT) {
+            const int nj = min(VT, j1 - js + 1);
+            __syncthreads();                                 // the last staged rows have been read
+            if (vec_v) {
+                constexpr int PER = 16 / int(sizeof(T));
+                const int per_row = dv / PER;
+                for (int i = tid; i < nj * per_row; i += KC) {
+                    const int jj = i / per_row, e = (i - jj * per_row) * PER;
+                    *reinterpret_cast<uint4*>(vt + jj * dv + e) = *reinterpret_cast<const uint4*>(cache + rowoff[js + jj] * dk + e);
+                }
+            } else {
+                for (int i = tid; i < nj * dv; i += KC) {
+                    const int jj = i / dv, e = i - jj * dv;
+                    vt[jj * dv + e] = cache[rowoff[js + jj] * dk + e];
+                }
+            }
+            __syncthreads();
+#pragma unroll 2
+            for (int jj = 0; jj < nj; jj++) {
+                float vv[NC];
+#pragma unroll
+                for (int c = 0; c < NC; c++) vv[c] = tid + c * KC < dv ? ib::to_f32(vt[jj * dv + tid + c * KC]) : 0.0f;
+#pragma unroll
+                for (int gq = 0; gq < GB; gq++) {
+                    const float pj = sc[gq * KC + js + jj];
+#pragma unroll
+                    for (int c = 0; c < NC; c++) o[gq][c] = fmaf(pj, vv[c], o[gq][c]);
+                }
+            }
+        }
+#pragma unroll
+        for (int gq = 0; gq < GB; gq++) {
+            float a, b;
+            merge_state(M[gq], L[gq], ml[2 * gq], ml[2 * gq + 1], a, b);
+#pragma unroll
+            for (int c = 0; c < NC; c++) O[gq][c] = merge_value(O[gq][c], a, o[gq][c], b);
+        }
+        __syncthreads();                                     // sc, ml and rowoff are free for the next chunk
+    }
+    if (n_splits > 1) {
+#pragma unroll
+        for (int gq = 0; gq < GB; gq++) {
+            if (gq < ng) {
+                float* dst = parts + ((t * n_heads + h0 + gq) * n_splits + blockIdx.z) * int64_t(dv + 2);
+                if (tid == 0) { dst[0] = M[gq]; dst[1] = L[gq]; }
+#pragma unroll
+                for (int c = 0; c < NC; c++)
+                    if (tid + c * KC < dv) dst[2 + tid + c * KC] = O[gq][c];
+            }
+        }
+        return;
+    }
+#pragma unroll
+    for (int gq = 0; gq < GB; gq++) {
+        if (gq < ng) {
+            const float inv = L[gq] > 0.0f ? 1.0f / L[gq] : 0.0f;
+#pragma unroll
+            for (int c = 0; c < NC; c++)
+                if (tid + c * KC < dv) out[(t * n_heads + h0 + gq) * dv + tid + c * KC] = ib::from_f32<T>(O[gq][c] * inv);
+        }
+    }
+}
+
+// One warp per (token, head): the chunks' parts merged in ascending order, then the division.
+template <typename T>
+__global__ void latent_attention_merge_kernel(const float* __restrict__ parts, const int* __restrict__ positions,
+                                              T* __restrict__ out, int64_t n_rows, int n_heads, int dv, int window, int n_splits) {
+    ib::pdl_wait();
+    const int lane = threadIdx.x & 31;
+    const int64_t r = int64_t(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (r >= n_rows) return;
+    const int pos = positions[r / n_heads];
+    const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+    const int n = min(n_splits, pos / KC - lo / KC + 1);
+    const float* mine = parts + r * n_splits * int64_t(dv + 2);
+    for (int c = lane; c < dv; c += 32) {
+        float M = -INFINITY, L = 0.0f, O = 0.0f;
+        for (int i = 0; i < n; i++) {
+            const float* p = mine + i * int64_t(dv + 2);
+            float a, b;
+            merge_state(M, L, p[0], p[1], a, b);
+            O = merge_value(O, a, p[2 + c], b);
+        }
+        out[r * dv + c] = ib::from_f32<T>(O * (L > 0.0f ? 1.0f / L : 0.0f));
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// A head's value up-projection on its latent context, the head's gate and a constant:
+//   out[t, h * dv + e] = mult * sigmoid(gates[t, gate_col + h]) * sum_r ctx[t, h, r] * w_uvT[h, r, e]
+// (gate_col < 0: no gate). w_uvT is the up-projection transposed per head, so that neighbouring threads read
+// neighbouring values. One CTA per (LO_TOK tokens, head); its 128 threads are ev channels x 128 / ev slices of r
+// (ev a power of two >= dv, at most 128); slice sums are added in slice order.
+constexpr int LO_TOK = 8, LO_THREADS = 128;
+
+template <typename T>
+__global__ void __launch_bounds__(LO_THREADS)
+latent_output_kernel(const T* __restrict__ ctx, const T* __restrict__ w_uvT, const float* __restrict__ gates, int64_t gate_ld,
+                     int gate_col, float mult, T* __restrict__ out, int64_t n_tokens, int n_heads, int R, int dv, int ev) {
+    ib::pdl_wait();
+    extern __shared__ float lo_sm[];
+    float* cs = lo_sm;                                // [LO_TOK][R]
+    float* red = cs + LO_TOK * R;                     // [slices][LO_TOK][ev]
+    const int64_t t0 = int64_t(blockIdx.x) * LO_TOK;
+    const int h = blockIdx.y, tid = threadIdx.x;
+    const int nt = int(min(int64_t(LO_TOK), n_tokens - t0));
+    for (int i = tid; i < LO_TOK * R; i += LO_THREADS) {
+        const int tt = i / R, r = i - tt * R;
+        cs[i] = tt < nt ? ib::to_f32(ctx[((t0 + tt) * n_heads + h) * R + r]) : 0.0f;
+    }
+    __syncthreads();
+    const int slices = LO_THREADS / ev, e = tid % ev, sl = tid / ev;
+    for (int e0 = 0; e0 < dv; e0 += ev) {
+        const int ee = e0 + e;
+        float acc[LO_TOK];
+#pragma unroll
+        for (int tt = 0; tt < LO_TOK; tt++) acc[tt] = 0.0f;
+        if (ee < dv) {
+            const T* w = w_uvT + int64_t(h) * R * dv + ee;
+            for (int r = sl; r < R; r += slices) {
+                const float wv = ib::to_f32(w[int64_t(r) * dv]);
+#pragma unroll
+                for (int tt = 0; tt < LO_TOK; tt++) acc[tt] = fmaf(cs[tt * R + r], wv, acc[tt]);
+            }
+        }
+#pragma unroll
+        for (int tt = 0; tt < LO_TOK; tt++) red[(sl * LO_TOK + tt) * ev + e] = acc[tt];
+        __syncthreads();
+        if (sl == 0 && ee < dv) {
+            for (int tt = 0; tt < nt; tt++) {
+                float s = 0.0f;
+                for (int k = 0; k < slices; k++) s += red[(k * LO_TOK + tt) * ev + e];
+                const int64_t t = t0 + tt;
+                const float gate = gate_col >= 0 ? sigmoid_(gates[t * gate_ld + gate_col + h]) : 1.0f;
+                out[(t * n_heads + h) * dv + ee] = ib::from_f32<T>(s * gate * mult);
+            }
+        }
+        __syncthreads();
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// Router with sigmoid scores. s = sigmoid(logit); the `top` experts with the largest s + correction are chosen (of
+// equal ones the lower index); weights[t, e] = mult * s for a chosen expert and 0 for the others. One warp per token.
+constexpr int RT_WARPS = 4;
+
+__global__ void __launch_bounds__(RT_WARPS * 32)
+route_sigmoid_kernel(const float* __restrict__ logits, const float* __restrict__ correction, int64_t n_tokens, int E, int top,
+                     float mult, float* __restrict__ weights, int* __restrict__ chosen) {
+    ib::pdl_wait();
+    extern __shared__ float rt_sm[];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int64_t t = int64_t(blockIdx.x) * RT_WARPS + warp;
+    if (t >= n_tokens) return;
+    float* score = rt_sm + warp * 2 * E;              // [E] sigmoid scores
+    float* choice = score + E;                        // [E] score + correction; -inf once chosen
+    for (int e = lane; e < E; e += 32) {
+        const float s = sigmoid_(logits[t * E + e]);
+        score[e] = s;
+        choice[e] = s + (correction ? correction[e] : 0.0f);
+        weights[t * E + e] = 0.0f;
+    }
+    __syncwarp();
+    for (int k = 0; k < top; k++) {
+        float best = -INFINITY;
+        int bi = E;
+        for (int e = lane; e < E; e += 32) {
+            const float c = choice[e];
+            if (c > best) { best = c; bi = e; }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (ob > best || (ob == best && oi < bi)) { best = ob; bi = oi; }
+        }
+        if (bi >= E) break;                           // nothing left to choose (NaN or -inf everywhere)
+        if (lane == 0) {
+            weights[t * E + bi] = score[bi] * mult;
+            if (chosen) chosen[t * top + k] = bi;
+            choice[bi] = -INFINITY;
+        }
+        __syncwarp();
+    }
+}
+
+// Hidden layer of ungated experts: out[t, j] = relu(x[t, j])^2 * scale[t, j / block] (scale absent: 1).
+template <typename T>
+__global__ void scaled_relu_sq_kernel(const T* __restrict__ x, const float* __restrict__ scale, int64_t n_tokens, int64_t width,
+                                      int64_t block, int64_t n_blocks, T* __restrict__ out) {
+    ib::pdl_wait();
+    const int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i >= n_tokens * width) return;
+    const int64_t t = i / width, j = i - t * width;
+    const float v = fmaxf(ib::to_f32(x[i]), 0.0f);
+    const float s = scale ? scale[t * n_blocks + j / block] : 1.0f;
+    out[i] = ib::from_f32<T>(v * v * s);
+}
+
+// Eight bfloat16 values a thread (width and block multiples of 8). A block whose scale is zero is not read.
+__global__ void scaled_relu_sq_vec_kernel(const bf16* __restrict__ x, const float* __restrict__ scale, int64_t n_tokens, int64_t width8,
+                                          int64_t block8, int64_t n_blocks, bf16* __restrict__ out) {
+    ib::pdl_wait();
+    const int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i >= n_tokens * width8) return;
+    const int64_t t = i / width8, j = i - t * width8;
+    const float s = scale ? scale[t * n_blocks + j / block8] : 1.0f;
+    uint4 r = make_uint4(0u, 0u, 0u, 0u);
+    if (s != 0.0f) {
+        const uint4 u = reinterpret_cast<const uint4*>(x)[i];
+        const __nv_bfloat162* hv = reinterpret_cast<const __nv_bfloat162*>(&u);
+        __nv_bfloat162* ho = reinterpret_cast<__nv_bfloat162*>(&r);
+#pragma unroll
+        for (int k = 0; k < 4; k++) {
+            const float2 f = __bfloat1622float2(hv[k]);
+            const float a = fmaxf(f.x, 0.0f), b = fmaxf(f.y, 0.0f);
+            ho[k] = __floats2bfloat162_rn(a * a * s, b * b * s);
+        }
+    }
+    reinterpret_cast<uint4*>(out)[i] = r;
+}
+
+__global__ void scale_softcap_kernel(float* __restrict__ x, int64_t n, float scale, float cap) {
+    ib::pdl_wait();
+    const int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const float v = x[i] * scale;
+    x[i] = cap > 0.0f ? cap * tanhf(v / cap) : v;
+}
+
+template <typename K>
+int allow_smem(K kernel, size_t bytes) {
+    if (bytes <= 48 * 1024) return IB_OK;
+    const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(bytes));
+    if (e != cudaSuccess) return ib::fail(IB_ERR_CUDA, "shared memory of %zu bytes: %s", bytes, cudaGetErrorString(e));
+    return IB_OK;
+}
+
+}  // namespace
+
+IB_EXPORT int ib_layer_norm(const float* x, const float* w, float eps, int64_t n_rows, int64_t hidden, const int* rows, void* out,
+                            int dtype, cudaStream_t stream) {
+    if (n_rows <= 0) return IB_OK;
+    if (hidden <= 0 || hidden > 48 * 1024 / 4) return ib::fail(IB_ERR_ARG, "ib_layer_norm: rows of %lld values are outside 1..12288", (long long)hidden);
+    const size_t smem = size_t(hidden) * sizeof(float);
+    if (dtype == IB_F32)
+        IB_LAUNCH(layer_norm_kernel<float>, unsigned(n_rows), LN_THREADS, smem, x, w, eps, hidden, rows, (float*)out);
+    else if (dtype == IB_BF16)
+        IB_LAUNCH(layer_norm_kernel<bf16>, unsigned(n_rows), LN_THREADS, smem, x, w, eps, hidden, rows, (bf16*)out);
+    else
+        return ib::fail(IB_ERR_ARG, "ib_layer_norm: unknown dtype %d", dtype);
+    return ib::check_launch("ib_layer_norm");
+}
+
+IB_EXPORT int ib_latent_prepare(const float* rows, int64_t ld, int q_col, int q_rank, int kv_col, int kv_rank, int rot_dim,
+                                const float* wq, const float* wkv, float eps, const float* cos_t, const float* sin_t, int layout,
+                                int n_rot, const int* positions, const int* token_seg, const int* block_table, int64_t max_blocks,
+                                void* cq, void* cache, int page_size, int64_t n_pages, int write, int64_t n_tokens, int dtype,
+                                int* status, cudaStream_t stream) {
+    if (n_tokens <= 0) return IB_OK;
+    if (n_rot < 0 || n_rot % 2 || n_rot > rot_dim) return ib::fail(IB_ERR_ARG, "ib_latent_prepare: %d rotated channels of %d", n_rot, rot_dim);
+    if (q_rank < 0 || (write && kv_rank <= 0)) return ib::fail(IB_ERR_ARG, "ib_latent_prepare: ranks %d / %d", q_rank, kv_rank);
+    if (dtype == IB_F32)
+        IB_LAUNCH(latent_prepare_kernel<float>, unsigned(n_tokens), LP_THREADS, 0, rows, ld, q_col, q_rank, kv_col, kv_rank, rot_dim, wq, wkv,
+                  eps, cos_t, sin_t, layout, n_rot, positions, token_seg, block_table, max_blocks, (float*)cq, (float*)cache, page_size,
+                  n_pages, write, status);
+    else if (dtype == IB_BF16)
+        IB_LAUNCH(latent_prepare_kernel<bf16>, unsigned(n_tokens), LP_THREADS, 0, rows, ld, q_col, q_rank, kv_col, kv_rank, rot_dim, wq, wkv,
+                  eps, cos_t, sin_t, layout, n_rot, positions, token_seg, block_table, max_blocks, (bf16*)cq, (bf16*)cache, page_size,
+                  n_pages, write, status);
+    else
+        return ib::fail(IB_ERR_ARG, "ib_latent_prepare: unknown dtype %d", dtype);
+    return ib::check_launch("ib_latent_prepare");
+}
+
+IB_EXPORT int ib_latent_query(const void* q, const void* w_uk, const float* cos_t, const float* sin_t, int layout, int n_rot,
+                              const int* positions, void* out, int64_t n_tokens, int n_heads, int d, int dr, int R, int dtype,
+                              cudaStream_t stream) {
+    if (n_tokens <= 0) return IB_OK;
+    if (n_heads <= 0 || n_heads > 65535 || d <= 0 || dr < 0 || R <= 0 || n_rot < 0 || n_rot % 2 || n_rot > dr)
+        return ib::fail(IB_ERR_ARG, "ib_latent_query: sizes heads %d, %d + %d channels, rank %d, %d rotated", n_heads, d, dr, R, n_rot);
+    const size_t smem = size_t(LQ_TOK) * d * sizeof(float);
+    if (smem > 48 * 1024) return ib::fail(IB_ERR_ARG, "ib_latent_query: heads of %d unrotated channels are too long", d);
+    const dim3 grid{blocks_for(n_tokens, LQ_TOK), unsigned(n_heads), blocks_for(R, LQ_THREADS)};
+    if (dtype == IB_F32)
+        IB_LAUNCH(latent_query_kernel<float>, grid, LQ_THREADS, smem, (const float*)q, (const float*)w_uk, cos_t, sin_t, layout, n_rot,
+                  positions, (float*)out, n_tokens, n_heads, d, dr, R);
+    else if (dtype == IB_BF16)
+        IB_LAUNCH(latent_query_kernel<bf16>, grid, LQ_THREADS, smem, (const bf16*)q, (const bf16*)w_uk, cos_t, sin_t, layout, n_rot,
+                  positions, (bf16*)out, n_tokens, n_heads, d, dr, R);
+    else
+        return ib::fail(IB_ERR_ARG, "ib_latent_query: unknown dtype %d", dtype);
+    return ib::check_launch("ib_latent_query");
+}
+
+IB_EXPORT int ib_latent_attention_max_dims(int* dk, int* dv) {
+    *dk = 1024;
+    *dv = 4 * KC;
+    return IB_OK;
+}
+
+namespace {
+template <typename T, int GB, int NC>
+int launch_latent_attention(const void* q, const void* cache, const int* block_table, int64_t max_blocks, const int* token_seg,
+                            const int* positions, void* out, float* parts, int64_t n_tokens, int n_heads, int group, int dk, int dv,
+                            int page_size, int window, float scale, int64_t n_pages, int n_splits, int* status, cudaStream_t stream) {
+    const int dq = (dk + 3) & ~3;
+    const size_t smem = size_t(GB * dq + GB * KC + 2 * GMAX) * sizeof(float) + KC * sizeof(int64_t) + size_t(VT) * dv * sizeof(T);
+    const int rc = allow_smem(latent_attention_kernel<T, GB, NC>, smem);
+    if (rc) return rc;
+    const int vec = dk % 8 == 0, vec_v = vec && (dv * sizeof(T)) % 16 == 0;
+    const dim3 grid{unsigned(n_tokens), unsigned((n_heads + group - 1) / group), unsigned(n_splits)};
+    IB_LAUNCH((latent_attention_kernel<T, GB, NC>), grid, KC, smem, (const T*)q, (const T*)cache, block_table, max_blocks, token_seg,
+              positions, (T*)out, parts, n_heads, group, dk, dv, page_size, window, scale, n_pages, n_splits, vec, vec_v, status);
+    return IB_OK;
+}
+
+template <typename T>
+int pick_latent_attention(int gb, int nc, const void* q, const void* cache, const int* block_table, int64_t max_blocks,
+                          const int* token_seg, const int* positions, void* out, float* parts, int64_t n_tokens, int n_heads, int group,
+                          int dk, int dv, int page_size, int window, float scale, int64_t n_pages, int n_splits, int* status,
+                          cudaStream_t stream) {
+#define IB_LA(GB_, NC_)                                                                                                      \
+    if (gb == GB_ && nc == NC_)                                                                                              \
+        return launch_latent_attention<T, GB_, NC_>(q, cache, block_table, max_blocks, token_seg, positions, out, parts, n_tokens, \
+                                                    n_heads, group, dk, dv, page_size, window, scale, n_pages, n_splits, status, stream);
+    IB_LA(1, 1) IB_LA(1, 2) IB_LA(1, 4) IB_LA(2, 1) IB_LA(2, 2) IB_LA(2, 4) IB_LA(4, 1) IB_LA(4, 2) IB_LA(4, 4) IB_LA(8, 1) IB_LA(8, 2) IB_LA(8, 4)
+#undef IB_LA
+    return ib::fail(IB_ERR_ARG, "ib_latent_attention: no kernel for groups of %d heads and %d channel passes", gb, nc);
+}
+}  // namespace
+
+// n_splits 1: one CTA per (token, group of heads) walks the token's chunks. n_splits > 1: a token's chunks are spread
+// over CTAs; `parts` holds n_tokens * n_heads * n_splits * (dv + 2) floats and the merge kernel follows. n_splits must
+// then be at least the number of chunks any token of the step reads.
+IB_EXPORT int ib_latent_attention(const void* q, const void* cache, const int* block_table, int64_t max_blocks, const int* token_seg,
+                                  const int* positions, void* out, float* parts, int64_t n_tokens, int n_heads, int dk, int dv,
+                                  int page_size, int window, float scale, int64_t n_pages, int n_splits, int dtype, int* status,
+                                  cudaStream_t stream) {
+    if (n_tokens <= 0) return IB_OK;
+    if (n_heads <= 0 || dk <= 0 || dk > 1024 || dv <= 0 || dv > dk || dv > 4 * KC)
+        return ib::fail(IB_ERR_ARG, "ib_latent_attention: %d heads, rows of %d with values of %d are outside what the kernel takes", n_heads, dk, dv);
+    if (n_splits < 1 || (n_splits > 1 && !parts)) return ib::fail(IB_ERR_ARG, "ib_latent_attention: %d splits need a workspace", n_splits);
+    if (n_splits > 65535 || (n_heads + GMAX - 1) / GMAX > 65535) return ib::fail(IB_ERR_ARG, "ib_latent_attention: grid too large");
+    const int group = n_heads < GMAX ? n_heads : GMAX;
+    const int gb = group <= 1 ? 1 : group <= 2 ? 2 : group <= 4 ? 4 : 8;
+    const int passes = (dv + KC - 1) / KC, nc = passes <= 1 ? 1 : passes <= 2 ? 2 : 4;
+    int rc;
+    if (dtype == IB_F32)
+        rc = pick_latent_attention<float>(gb, nc, q, cache, block_table, max_blocks, token_seg, positions, out, parts, n_tokens, n_heads,
+                                          group, dk, dv, page_size, window, scale, n_pages, n_splits, status, stream);
+    else if (dtype == IB_BF16)
+        rc = pick_latent_attention<bf16>(gb, nc, q, cache, block_table, max_blocks, token_seg, positions, out, parts, n_tokens, n_heads,
+                                         group, dk, dv, page_size, window, scale, n_pages, n_splits, status, stream);
+    else
+        return ib::fail(IB_ERR_ARG, "ib_latent_attention: unknown dtype %d", dtype);
+    if (rc) return rc;
+    if (n_splits > 1) {
+        const int64_t n_rows = n_tokens * n_heads;
+        if (dtype == IB_F32)
+            IB_LAUNCH(latent_attention_merge_kernel<float>, blocks_for(n_rows, 4), 128, 0, parts, positions, (float*)out, n_rows, n_heads, dv,
+                      window, n_splits);
+        else
+            IB_LAUNCH(latent_attention_merge_kernel<bf16>, blocks_for(n_rows, 4), 128, 0, parts, positions, (bf16*)out, n_rows, n_heads, dv,
+                      window, n_splits);
+    }
+    return ib::check_launch("ib_latent_attention");
+}
+
+IB_EXPORT int ib_latent_output(const void* ctx, const void* w_uvT, const float* gates, int64_t gate_ld, int gate_col, float mult,
+                               void* out, int64_t n_tokens, int n_heads, int R, int dv, int dtype, cudaStream_t stream) {
+    if (n_tokens <= 0) return IB_OK;
+    if (n_heads <= 0 || n_heads > 65535 || R <= 0 || dv <= 0) return ib::fail(IB_ERR_ARG, "ib_latent_output: sizes %d heads, rank %d, values %d", n_heads, R, dv);
+    int ev = 1;
+    while (ev < dv && ev < LO_THREADS) ev *= 2;
+    const size_t smem = size_t(LO_TOK) * R * sizeof(float) + size_t(LO_THREADS) * LO_TOK * sizeof(float);
+    if (smem > 48 * 1024) return ib::fail(IB_ERR_ARG, "ib_latent_output: a rank of %d is too large", R);
+    const dim3 grid{blocks_for(n_tokens, LO_TOK), unsigned(n_heads), 1u};
+    if (dtype == IB_F32)
+        IB_LAUNCH(latent_output_kernel<float>, grid, LO_THREADS, smem, (const float*)ctx, (const float*)w_uvT, gates, gate_ld, gate_col, mult,
+                  (float*)out, n_tokens, n_heads, R, dv, ev);
+    else if (dtype == IB_BF16)
+        IB_LAUNCH(latent_output_kernel<bf16>, grid, LO_THREADS, smem, (const bf16*)ctx, (const bf16*)w_uvT, gates, gate_ld, gate_col, mult,
+                  (bf16*)out, n_tokens, n_heads, R, dv, ev);
+    else
+        return ib::fail(IB_ERR_ARG, "ib_latent_output: unknown dtype %d", dtype);
+    return ib::check_launch("ib_latent_output");
+}
+
+IB_EXPORT int ib_route_sigmoid(const float* logits, const float* correction, int64_t n_tokens, int E, int top, float mult,
+                               float* weights, int* chosen, cudaStream_t stream) {
+    if (n_tokens <= 0) return IB_OK;
+    if (E <= 0 || top <= 0 || top > E || E > 1024) return ib::fail(IB_ERR_ARG, "ib_route_sigmoid: %d of %d experts", top, E);
+    IB_LAUNCH(route_sigmoid_kernel, blocks_for(n_tokens, RT_WARPS), RT_WARPS * 32, size_t(RT_WARPS) * 2 * E * sizeof(float), logits, correction,
+              n_tokens, E, top, mult, weights, chosen);
+    return ib::check_launch("ib_route_sigmoid");
+}
+
+IB_EXPORT int ib_scaled_relu_sq(const void* x, const float* scale, int64_t n_tokens, int64_t width, int64_t block, int64_t n_blocks,
+                                void* out, int dtype, cudaStream_t stream) {
+    if (n_tokens <= 0 || width <= 0) return IB_OK;
+    if (scale && (block <= 0 || n_blocks * block < width)) return ib::fail(IB_ERR_ARG, "ib_scaled_relu_sq: %lld blocks of %lld do not cover %lld columns",
+                                                                            (long long)n_blocks, (long long)block, (long long)width);
+    if (!scale) { block = width; n_blocks = 1; }
+    const int64_t n = n_tokens * width;
+    if (dtype == IB_F32)
+        IB_LAUNCH(scaled_relu_sq_kernel<float>, blocks_for(n, 256), 256, 0, (const float*)x, scale, n_tokens, width, block, n_blocks, (float*)out);
+    else if (dtype == IB_BF16) {
+        if (width % 8 == 0 && block % 8 == 0)
+            IB_LAUNCH(scaled_relu_sq_vec_kernel, blocks_for(n / 8, 256), 256, 0, (const bf16*)x, scale, n_tokens, width / 8, block / 8, n_blocks, (bf16*)out);
+        else
+            IB_LAUNCH(scaled_relu_sq_kernel<bf16>, blocks_for(n, 256), 256, 0, (const bf16*)x, scale, n_tokens, width, block, n_blocks, (bf16*)out);
+    } else
+        return ib::fail(IB_ERR_ARG, "ib_scaled_relu_sq: unknown dtype %d", dtype);
+    return ib::check_launch("ib_scaled_relu_sq");
+}
+
+IB_EXPORT int ib_scale_softcap(float* x, int64_t n, float scale, float cap, cudaStream_t stream) {
+    if (n <= 0) return IB_OK;
+    IB_LAUNCH(scale_softcap_kernel, blocks_for(n, 256), 256, 0, x, n, scale, cap);
+    return ib::check_launch("ib_scale_softcap");
+}

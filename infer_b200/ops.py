@@ -782,3 +782,175 @@ def head_norm_gate(o: torch.Tensor, weight: torch.Tensor, eps: float, gate: Opti
     _call(f, o.data_ptr(), weight.data_ptr(), float(eps), _ptr(gate), ldg, int(gate_col),
           dtype_code(gate.dtype) if gate is not None else 0, out.data_ptr(), dtype_code(out_dtype), T, n_heads, v_dim, _stream())
     return out
+
+
+# ----------------------------------------------------------------------------- attention through low-rank latents
+
+def layer_norm(x: torch.Tensor, weight: torch.Tensor, eps: float, out_dtype: torch.dtype,
+               rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """(x - mean) / sqrt(mean of squared deviations + eps) * weight per float32 row; ``rows`` (int32) selects and
+    orders the input rows."""
+    _check(x, "x", torch.float32)
+    H = x.shape[-1]
+    _check(weight, "weight", torch.float32, (H,))
+    if rows is not None:
+        _check(rows, "rows", torch.int32)
+    n = rows.numel() if rows is not None else x.numel() // H
+    out = torch.empty((n, H), dtype=out_dtype, device=x.device)
+    f = _fn("latent", "ib_layer_norm", [c_void_p, c_void_p, c_float, c_int64, c_int64, c_void_p, c_void_p, c_int, c_void_p])
+    _call(f, x.data_ptr(), weight.data_ptr(), float(eps), n, H, _ptr(rows), out.data_ptr(), dtype_code(out_dtype), _stream())
+    return out
+
+
+ROTATION_LAYOUTS = {"pairs": 0, "half": 1}
+
+
+def latent_prepare(rows: torch.Tensor, q_col: int, q_rank: int, kv_col: int, kv_rank: int, rot_dim: int,
+                   wq: Optional[torch.Tensor], wkv: Optional[torch.Tensor], eps: float, cos: Optional[torch.Tensor],
+                   sin: Optional[torch.Tensor], layout: str, step, block_table: torch.Tensor, cache: torch.Tensor,
+                   out_dtype: torch.dtype, write: bool = True) -> Optional[torch.Tensor]:
+    """Float32 rows of the down-projections -> the normalised query latent cq [T, q_rank] (None with q_rank 0) and,
+    with ``write``, each token's row [normalised kv latent | rotated shared key part] in its page of ``cache``
+    [pages, page_size, kv_rank + rot_dim]. The tables' width says how many channels of the shared part turn."""
+    _check(rows, "rows", torch.float32)
+    T, ld = rows.shape
+    n_pages, page_size, width = cache.shape
+    _check(cache, "cache", out_dtype, (n_pages, page_size, kv_rank + rot_dim))
+    if q_col < 0 or q_col + q_rank > ld or (write and (kv_col < 0 or kv_col + kv_rank + rot_dim > ld)):
+        raise KernelError("the latents lie outside the rows")
+    if q_rank:
+        _check(wq, "wq", torch.float32, (q_rank,))
+    if write:
+        _check(wkv, "wkv", torch.float32, (kv_rank,))
+    n_rot = 0
+    if cos is not None:
+        n_rot = 2 * cos.shape[1]
+        _check(cos, "cos", torch.float32)
+        _check(sin, "sin", torch.float32, tuple(cos.shape))
+    _check(block_table, "block_table", torch.int32)
+    cq = torch.empty((T, q_rank), dtype=out_dtype, device=rows.device) if q_rank else None
+    f = _fn("latent", "ib_latent_prepare", [c_void_p, c_int64] + [c_int] * 5 + [c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_int, c_int,
+                                            c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_int, c_int64, c_int, c_int64,
+                                            c_int, c_void_p, c_void_p])
+    _call(f, rows.data_ptr(), ld, int(q_col), int(q_rank), int(kv_col), int(kv_rank), int(rot_dim), _ptr(wq), _ptr(wkv), float(eps),
+          _ptr(cos), _ptr(sin), ROTATION_LAYOUTS[layout], n_rot, step.positions.data_ptr(), step.token_seg.data_ptr(),
+          block_table.data_ptr(), block_table.shape[1], _ptr(cq), cache.data_ptr(), page_size, n_pages, int(write), T,
+          dtype_code(out_dtype), _ptr(step.status), _stream())
+    return cq
+
+
+def latent_query(q: torch.Tensor, w_uk: torch.Tensor, cos: Optional[torch.Tensor], sin: Optional[torch.Tensor], layout: str,
+                 positions: torch.Tensor, n_heads: int, d: int, dr: int) -> torch.Tensor:
+    """q [T, heads * (d + dr)] and the key up-projection w_uk [heads * d, R] -> queries in the latent space
+    [T, heads, R + dr]: the unrotated channels carried through w_uk, the rotated ones turned by their position."""
+    _check(q, "q")
+    T = q.shape[0]
+    R = w_uk.shape[1]
+    _check(q, "q", None, (T, n_heads * (d + dr)))
+    _check(w_uk, "w_uk", q.dtype, (n_heads * d, R))
+    n_rot = 0
+    if cos is not None:
+        n_rot = 2 * cos.shape[1]
+        _check(cos, "cos", torch.float32)
+        _check(sin, "sin", torch.float32, tuple(cos.shape))
+    out = torch.empty((T, n_heads, R + dr), dtype=q.dtype, device=q.device)
+    f = _fn("latent", "ib_latent_query", [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int64,
+                                          c_int, c_int, c_int, c_int, c_int, c_void_p])
+    _call(f, q.data_ptr(), w_uk.data_ptr(), _ptr(cos), _ptr(sin), ROTATION_LAYOUTS[layout], n_rot, positions.data_ptr(), out.data_ptr(),
+          T, n_heads, d, dr, R, dtype_code(q.dtype), _stream())
+    return out
+
+
+def latent_attention_max_dims():
+    f = _fn("latent", "ib_latent_attention_max_dims", [ctypes.POINTER(c_int), ctypes.POINTER(c_int)])
+    a, b = c_int(0), c_int(0)
+    f(ctypes.byref(a), ctypes.byref(b))
+    return a.value, b.value
+
+
+LATENT_CHUNK = 128                 # keys of one chunk of the latent attention kernel
+
+
+def latent_attention(q: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor, step, dv: int, window: Optional[int],
+                     scale: float, split: Optional[bool] = None) -> torch.Tensor:
+    """q [T, heads, dk] over the rows ``cache`` [pages, page_size, dk] -> contexts [T, heads, dv]: a row's first dv
+    channels are its value. ``split``: spread a token's key chunks over CTAs (default: in steps of single tokens that
+    alone would not fill the device); the result's bits do not depend on it."""
+    _check(q, "q")
+    T, H, dk = q.shape
+    n_pages, page_size, _ = cache.shape
+    _check(cache, "cache", q.dtype, (n_pages, page_size, dk))
+    _check(block_table, "block_table", torch.int32)
+    span = step.max_ctx_len if not window else min(step.max_ctx_len, int(window) + LATENT_CHUNK - 1)
+    chunks = max(1, -(-span // LATENT_CHUNK) + (1 if window else 0))
+    if split is None:
+        split = step.decode_only and T * ((H + 7) // 8) < 256
+    n_splits = chunks if (split and chunks > 1) else 1
+    out = torch.empty((T, H, dv), dtype=q.dtype, device=q.device)
+    parts = None
+    if n_splits > 1:
+        from .fast_ops import device_state
+        parts = device_state(q.device).workspace(T * H * n_splits * (dv + 2))
+    f = _fn("latent", "ib_latent_attention", [c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_int64,
+                                              c_int, c_int, c_int, c_int, c_int, c_float, c_int64, c_int, c_int, c_void_p, c_void_p])
+    _call(f, q.data_ptr(), cache.data_ptr(), block_table.data_ptr(), block_table.shape[1], step.token_seg.data_ptr(),
+          step.positions.data_ptr(), out.data_ptr(), _ptr(parts), T, H, dk, int(dv), page_size, int(window or 0), float(scale),
+          n_pages, n_splits, dtype_code(q.dtype), _ptr(step.status), _stream())
+    return out
+
+
+def latent_output(ctx: torch.Tensor, w_uvT: torch.Tensor, gates: Optional[torch.Tensor], gate_col: int, mult: float) -> torch.Tensor:
+    """Latent contexts [T, heads, R] and the value up-projection transposed per head, w_uvT [heads, R, dv] ->
+    [T, heads * dv], each head times sigmoid(gates[t, gate_col + head]) (``gates`` float32 rows; None: no gate) and
+    times ``mult``."""
+    _check(ctx, "ctx")
+    T, H, R = ctx.shape
+    dv = w_uvT.shape[2]
+    _check(w_uvT, "w_uvT", ctx.dtype, (H, R, dv))
+    if gates is not None:
+        _check(gates, "gates", torch.float32)
+        if gates.shape[0] != T or gate_col < 0 or gate_col + H > gates.shape[1]:
+            raise KernelError("the gates lie outside their rows")
+    out = torch.empty((T, H * dv), dtype=ctx.dtype, device=ctx.device)
+    f = _fn("latent", "ib_latent_output", [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_float, c_void_p, c_int64, c_int, c_int, c_int,
+                                           c_int, c_void_p])
+    _call(f, ctx.data_ptr(), w_uvT.data_ptr(), _ptr(gates), gates.shape[1] if gates is not None else 0,
+          int(gate_col) if gates is not None else -1, float(mult), out.data_ptr(), T, H, R, dv, dtype_code(ctx.dtype), _stream())
+    return out
+
+
+def route_sigmoid(logits: torch.Tensor, correction: Optional[torch.Tensor], top: int, mult: float = 1.0, want_chosen: bool = False):
+    """Router on float32 logits [T, E] with sigmoid scores: the ``top`` experts with the largest score + correction
+    are chosen (of equal ones the lower index); a chosen expert's weight is its score times ``mult``, not renormalised.
+    Returns (weights float32 [T, E], zero where not chosen; chosen int32 [T, top] or None)."""
+    _check(logits, "logits", torch.float32)
+    T, E = logits.shape
+    if correction is not None:
+        _check(correction, "correction", torch.float32, (E,))
+    weights = torch.empty((T, E), dtype=torch.float32, device=logits.device)
+    chosen = torch.empty((T, top), dtype=torch.int32, device=logits.device) if want_chosen else None
+    f = _fn("latent", "ib_route_sigmoid", [c_void_p, c_void_p, c_int64, c_int, c_int, c_float, c_void_p, c_void_p, c_void_p])
+    _call(f, logits.data_ptr(), _ptr(correction), T, E, int(top), float(mult), weights.data_ptr(), _ptr(chosen), _stream())
+    return weights, chosen
+
+
+def scaled_relu_sq(x: torch.Tensor, scale: Optional[torch.Tensor] = None, block: int = 0) -> torch.Tensor:
+    """relu(x)^2 per element of x [T, width]; with ``scale`` float32 [T, n]: block e of ``block`` columns times scale[t, e]."""
+    _check(x, "x")
+    T, width = x.shape
+    n_blocks = 0
+    if scale is not None:
+        n_blocks = scale.shape[1]
+        _check(scale, "scale", torch.float32, (T, n_blocks))
+    out = torch.empty_like(x)
+    f = _fn("latent", "ib_scaled_relu_sq", [c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_void_p, c_int, c_void_p])
+    _call(f, x.data_ptr(), _ptr(scale), T, width, int(block), n_blocks, out.data_ptr(), dtype_code(x.dtype), _stream())
+    return out
+
+
+def scale_softcap(logits: torch.Tensor, scale: float, cap: float) -> torch.Tensor:
+    """In place on float32 logits: cap * tanh(logits * scale / cap); cap 0: the scale alone."""
+    _check(logits, "logits", torch.float32)
+    f = _fn("latent", "ib_scale_softcap", [c_void_p, c_int64, c_float, c_float, c_void_p])
+    _call(f, logits.data_ptr(), logits.numel(), float(scale), float(cap), _stream())
+    return logits

@@ -27,10 +27,18 @@ class PagedKVNeed:
     head_dim: int
     window: Optional[int] = None     # None: all positions stay; n: only the last n are ever read
     v_head_dim: Optional[int] = None  # size of a value where it differs from a key's (None: head_dim)
+    values_in_keys: bool = False      # True: a position's value is the first v_head_dim channels of its key row (one
+                                      # row per position serves both, as in attention through a shared latent); there
+                                      # are no value pages and the view's ``v`` is None
 
     @property
     def value_dim(self) -> int:
         return int(self.v_head_dim or self.head_dim)
+
+    @property
+    def stored_value_dim(self) -> int:
+        """Channels per position and kv head that the value pages hold."""
+        return 0 if self.values_in_keys else self.value_dim
 
 
 @dataclass(frozen=True)

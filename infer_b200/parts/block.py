@@ -1,6 +1,7 @@
 """Arrangements of parts into a layer. "prenorm": h += mixer(norm(h)); h += feed_forward(norm(h))
-(src/forward.cpp:200-244), over the slots mixer_norm, mixer, feed_forward_norm, feed_forward. The residual stream h
-is float32; the sums happen in the parts' last matrix product, in float32.
+(src/forward.cpp:200-244), over the slots mixer_norm, mixer, feed_forward_norm, feed_forward (the last two may be
+absent together: a layer without feed-forward). The residual stream h is float32; the sums happen in the parts'
+last matrix product, in float32.
 
 "parallel_gated": ONE norm, whose rows n = norm(h) every sublayer reads, and one sum:
 h += sigmoid(G1 n + g1) * mixer(n) + sigmoid(G2 n + g2) * feed_forward(n); the feed-forward (and its gate) may be
@@ -50,11 +51,19 @@ def normed_input(norm, consumer, h):
 
 @register_block("prenorm")
 class PreNormBlock(Block):
-    def __init__(self, mixer_norm, mixer, feed_forward_norm, feed_forward):
-        super().__init__(mixer_norm=mixer_norm, mixer=mixer, feed_forward_norm=feed_forward_norm, feed_forward=feed_forward)
+    def __init__(self, mixer_norm, mixer, feed_forward_norm=None, feed_forward=None):
+        if (feed_forward is None) != (feed_forward_norm is None):
+            raise ValueError("a prenorm block has a feed-forward and its norm, or neither")
+        parts = {"mixer_norm": mixer_norm, "mixer": mixer}
+        if feed_forward is not None:
+            parts.update(feed_forward_norm=feed_forward_norm, feed_forward=feed_forward)
+        super().__init__(**parts)
+        self.feed_forward_norm, self.feed_forward = feed_forward_norm, feed_forward
 
     def forward(self, h, step, cache, write_cache=True):
         h = self.mixer.forward(normed_input(self.mixer_norm, self.mixer, h), step, cache, h, write_cache)
+        if self.feed_forward is None:
+            return h
         return self.feed_forward.forward(normed_input(self.feed_forward_norm, self.feed_forward, h), h)
 
 

@@ -95,3 +95,69 @@ class RotaryPairs(PositionEncoding):
 
     def apply(self, q, k, positions):
         raise NotImplementedError("rotary_pairs is applied by the attention part's prepare kernel")
+
+
+def interpolated_frequencies(rotary_dims: int, theta: float, scaling):
+    """(frequencies float64 [rotary_dims / 2], magnitude). f_i = theta^(-2i / rotary_dims). With ``scaling`` {factor,
+    original, fast, slow} (YaRN): pairs that turn fast keep f_i, pairs that turn slowly take f_i / factor, a linear
+    ramp between, which runs from the pair index at which a full turn takes original / fast positions to the one
+    at which it takes original / slow positions (index(t) = rotary_dims * ln(original / (2 pi t)) / (2 ln theta),
+    the lower end rounded down and not below 0, the upper rounded up and not above rotary_dims - 1); cosines and
+    sines are multiplied by ``magnitude_slope`` * ln(factor) + 1."""
+    import math
+    i = torch.arange(rotary_dims // 2, dtype=torch.float64)
+    f = torch.pow(torch.tensor(float(theta), dtype=torch.float64), -2.0 * i / float(rotary_dims))
+    if not scaling:
+        return f, 1.0
+    factor, original = float(scaling["factor"]), float(scaling["original"])
+
+    def index_of(turns: float) -> float:
+        return rotary_dims * math.log(original / (2.0 * math.pi * turns)) / (2.0 * math.log(theta))
+    lo = max(math.floor(index_of(float(scaling["fast"]))), 0)
+    hi = min(math.ceil(index_of(float(scaling["slow"]))), rotary_dims - 1)
+    ramp = torch.clamp((i - lo) / max(hi - lo, float(scaling.get("min_span", 0.001))), 0.0, 1.0)
+    return f / factor * ramp + f * (1.0 - ramp), float(scaling.get("magnitude_slope", 0.1)) * math.log(factor) + 1.0
+
+
+@register_position("rotary_interpolated")
+class RotaryInterpolated(PositionEncoding):
+    """A rotation over the first ``rotary_dims`` channels of what it is applied to, in either layout ("pairs":
+    channel 2i with 2i + 1; "half": channel i with i + rotary_dims / 2), with optionally interpolated frequencies
+    (``scaling``, see interpolated_frequencies). Angles, cosines and sines are computed in float64 on the host and
+    rounded once; the magnitude is part of the tables, so the kernels that apply them know nothing of the scaling."""
+
+    def __init__(self, spec: PartSpec, runtime):
+        super().__init__(spec, runtime)
+        self.theta = float(spec["theta"])
+        self.rotary_dims = int(spec["rotary_dims"])
+        self.head_dim = int(spec.get("head_dim") or self.rotary_dims)
+        self.layout = str(spec.get("layout", "half"))
+        self.scaling = dict(spec["scaling"]) if spec.get("scaling") else None
+        self.max_positions = int(spec["max_positions"])
+        if self.layout not in ("pairs", "half"):
+            raise ValueError(f"a rotation's layout is 'pairs' or 'half', not {self.layout!r}")
+        if self.rotary_dims <= 0 or self.rotary_dims % 2 or self.rotary_dims > self.head_dim:
+            raise ValueError(f"rotary_interpolated needs an even number of rotated channels within the head, got "
+                             f"{self.rotary_dims} of {self.head_dim}")
+        if self.theta <= 1:
+            raise ValueError("rotary_interpolated needs a theta above 1")
+        if self.scaling is not None:
+            for k in ("factor", "original", "fast", "slow"):
+                if k not in self.scaling or float(self.scaling[k]) <= 0:
+                    raise ValueError(f"rotary_interpolated: scaling needs a positive {k!r}")
+
+    def rotary_tables(self, n_positions: int = None):
+        n = min(self.max_positions, n_positions or self.max_positions)
+        sc = tuple(sorted(self.scaling.items())) if self.scaling else None
+        cache_key = ("interpolated", self.rotary_dims, self.theta, sc, n, str(self.rt.device))
+        t = _SHARED_TABLES.get(cache_key)
+        if t is None:
+            freq, mag = interpolated_frequencies(self.rotary_dims, self.theta, self.scaling)
+            angle = torch.arange(n, dtype=torch.float64)[:, None] * freq[None, :]
+            t = ((torch.cos(angle) * mag).to(torch.float32).to(self.rt.device).contiguous(),
+                 (torch.sin(angle) * mag).to(torch.float32).to(self.rt.device).contiguous())
+            _SHARED_TABLES[cache_key] = t
+        return t
+
+    def apply(self, q, k, positions):
+        raise NotImplementedError("rotary_interpolated is applied by the kernels of the mixer that names it")

@@ -17,6 +17,15 @@ needed ones).
 
 Tensors: ``router`` [experts, hidden]; per expert i ``e<i>.gate``, ``e<i>.up`` [ff, hidden], ``e<i>.down`` [hidden, ff];
 ``shared.gate`` / ``shared.up`` / ``shared.down`` likewise. No biases.
+
+Other forms, each a key of the spec:
+
+``router_kind``  "softmax_groups" (above) or "sigmoid": s = sigmoid(x Wr^T); the ``top`` experts with the largest
+                 s + correction are chosen (``correction`` [experts], a stored tensor that only the choice sees);
+                 weight_e = s_e as it is, not renormalised; no groups
+``expert_kind``  "clipped_swish_glu" (above) or "relu_squared": expert(x) = Wd relu(Wu x)^2, no gate matrix, no limit
+``out_scale``    a constant on the result (default 1), multiplied into the experts' weights in float32: a block's
+                 residual multiplier costs nothing this way
 """
 from __future__ import annotations
 
@@ -34,10 +43,20 @@ class RoutedExperts(FeedForward):
         super().__init__(spec, runtime)
         self.hidden, self.n_experts, self.top = int(spec["hidden_size"]), int(spec["experts"]), int(spec["top"])
         self.groups, self.keep = int(spec.get("groups") or 1), int(spec.get("keep") or 1)
-        self.ff, self.limit = int(spec["expert_size"]), float(spec["limit"])
+        self.ff, self.limit = int(spec["expert_size"]), float(spec.get("limit") or 0.0)
         self.shared_ff = int(spec.get("shared_size") or 0)
         self.shared_limit = float(spec.get("shared_limit") or 0.0)
         self.slope, self.sum_eps = float(spec.get("slope", 1.702)), float(spec.get("sum_eps", 1e-20))
+        self.router_kind = str(spec.get("router_kind", "softmax_groups"))
+        self.expert_kind = str(spec.get("expert_kind", "clipped_swish_glu"))
+        self.out_scale = float(spec.get("out_scale", 1.0))
+        if self.router_kind not in ("softmax_groups", "sigmoid") or self.expert_kind not in ("clipped_swish_glu", "relu_squared"):
+            raise ValueError(f"routed_experts: unknown router_kind {self.router_kind!r} or expert_kind {self.expert_kind!r}")
+        if self.router_kind == "sigmoid" and (self.groups != 1 or self.keep != 1):
+            raise ValueError("a sigmoid router has no groups")
+        if self.out_scale != 1.0 and (self.router_kind != "sigmoid" or self.shared_ff):
+            raise ValueError("out_scale goes into the weights of a sigmoid router and does not reach a shared expert")
+        self.correction = None
         if min(self.hidden, self.n_experts, self.top, self.groups, self.keep, self.ff) <= 0 or self.shared_ff < 0:
             raise ValueError("routed_experts needs positive sizes")
         if self.n_experts % self.groups or self.keep > self.groups or self.top > self.keep * (self.n_experts // self.groups):
@@ -47,17 +66,22 @@ class RoutedExperts(FeedForward):
     @classmethod
     def param_shapes(cls, spec):
         H, E, F, Fs = int(spec["hidden_size"]), int(spec["experts"]), int(spec["expert_size"]), int(spec.get("shared_size") or 0)
+        gated = str(spec.get("expert_kind", "clipped_swish_glu")) != "relu_squared"
         shapes = {"router": (E, H)}
-        for i in range(E):
-            shapes.update({f"e{i}.gate": (F, H), f"e{i}.up": (F, H), f"e{i}.down": (H, F)})
-        if Fs:
-            shapes.update({"shared.gate": (Fs, H), "shared.up": (Fs, H), "shared.down": (H, Fs)})
+        if str(spec.get("router_kind", "softmax_groups")) == "sigmoid":
+            shapes["correction"] = (E,)
+        for u, f in [(f"e{i}", F) for i in range(E)] + ([("shared", Fs)] if Fs else []):
+            shapes.update({u + ".up": (f, H), u + ".down": (H, f)})
+            if gated:
+                shapes[u + ".gate"] = (f, H)
         return shapes
 
     @classmethod
     def init_params(cls, spec, name, shape, gen):
         if name == "router":
             return 0.5 * torch.randn(shape, generator=gen, dtype=torch.float32, device=gen.device)
+        if name == "correction":
+            return 0.2 * torch.randn(shape, generator=gen, dtype=torch.float32, device=gen.device)
         return 0.1 * torch.randn(shape, generator=gen, dtype=torch.float32, device=gen.device)
 
     def load(self, params):
@@ -65,6 +89,13 @@ class RoutedExperts(FeedForward):
         shared = ["shared"] if self.shared_ff else []
         units = [f"e{i}" for i in range(E)] + shared
         self.router = Linear(self.rt, params["router"])
+        if self.router_kind == "sigmoid":
+            self.correction = params["correction"].to(device=self.rt.device, dtype=torch.float32).contiguous()
+        self.width = E * self.ff + self.shared_ff
+        if self.expert_kind == "relu_squared":
+            self.gate_up = Linear(self.rt, torch.cat([params[u + ".up"] for u in units], dim=0))
+            self.down = Linear(self.rt, torch.cat([params[u + ".down"] for u in units], dim=1))
+            return
         # result rows [gate of expert 0 | .. | gate of the shared expert | up of expert 0 | .. | up of the shared expert]
         self.gate_up = Linear(self.rt, torch.cat([params[u + ".gate"] for u in units] + [params[u + ".up"] for u in units], dim=0))
         self.down = Linear(self.rt, torch.cat([params[u + ".down"] for u in units], dim=1))
@@ -72,10 +103,18 @@ class RoutedExperts(FeedForward):
 
     def forward(self, x, residual):
         logits = self.router(x, out_dtype=torch.float32)
-        weights, _ = ops.route(logits, self.top, self.groups, self.keep, self.sum_eps)
+        if self.router_kind == "sigmoid":
+            weights, _ = ops.route_sigmoid(logits, self.correction, self.top, self.out_scale)
+        else:
+            weights, _ = ops.route(logits, self.top, self.groups, self.keep, self.sum_eps)
         rows = self.gate_up(x)
-        act = ops.glu_act(rows, 0, self.width, self.width, "clipped_swish", self.limit, self.shared_limit, self.slope,
-                          weights, self.ff, self.n_experts)
+        if self.expert_kind == "relu_squared":
+            if self.shared_ff:
+                raise NotImplementedError("a shared expert of the relu_squared form")
+            act = ops.scaled_relu_sq(rows, weights, self.ff)
+        else:
+            act = ops.glu_act(rows, 0, self.width, self.width, "clipped_swish", self.limit, self.shared_limit, self.slope,
+                              weights, self.ff, self.n_experts)
         if residual is None:
             return self.down(act, out_dtype=torch.float32)
         return self.down(act, residual=residual)

@@ -5,7 +5,8 @@ h[t, :] = float32(table[ids[t], :]), optionally times a constant ``scale`` (src/
 logits = x . W^T without bias, W being the head's own matrix or, when tied, the token table itself
 (src/forward.cpp:246-257, src/model.h:52). An architecture whose ends do more (a soft cap on the logits, a bias)
 registers its own ``Embedding`` / ``Head`` kinds; the model only calls ``forward``. ``weight_name`` in either spec
-renames the part's one tensor (default "weight") under its prefix. With ``norm_weight_name`` (and ``norm_eps``) the
+renames the part's one tensor (default "weight") under its prefix. A head with ``logit_scale`` and / or ``softcap``
+returns cap * tanh(logits * scale / cap) (the scale alone without a cap). With ``norm_weight_name`` (and ``norm_eps``) the
 looked-up rows are divided by their root mean square and multiplied by that weight before they enter the residual stream.
 """
 from __future__ import annotations
@@ -72,6 +73,10 @@ class LinearHead(Head):
         super().__init__(spec, runtime)
         self.vocab, self.hidden = int(spec["vocab_size"]), int(spec["hidden_size"])
         self.tied = bool(spec.get("tied", False))
+        self.logit_scale = float(spec.get("logit_scale") or 1.0)
+        self.softcap = float(spec.get("softcap") or 0.0)
+        if self.softcap < 0:
+            raise ValueError("a head's softcap must be positive (or absent)")
         self.linear = None
 
     @classmethod
@@ -91,4 +96,7 @@ class LinearHead(Head):
         self.linear = Linear.share(self.rt, table)
 
     def forward(self, x):
-        return self.linear(x, out_dtype=torch.float32)
+        logits = self.linear(x, out_dtype=torch.float32)
+        if self.logit_scale != 1.0 or self.softcap > 0:
+            ops.scale_softcap(logits, self.logit_scale, self.softcap)
+        return logits
