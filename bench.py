@@ -4,6 +4,7 @@ random weights on one B200.
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--context 2048] [--layers L] [--impl reference]
     python bench.py --design ruvenex [--sizes 1.5b|7b] [--layers L]     (another design beside Qwen2 at equal sizes)
     python bench.py --design fozerax [--sizes 1.5b|7b] [--layers L]     (beside Ruvenex, the closest design, and Qwen2)
+    python bench.py --design pefazen [--sizes 1.5b|7b] [--layers L]     (beside Fozerax, the closest design, and Qwen2)
 
 Prints ONE JSON line. "value" is decoded tokens per second of the step function, timed on the device with CUDA
 events around K decode steps of a batch of 8 requests whose 2,048-token contexts already lie in the paged cache
@@ -34,9 +35,10 @@ def _preset(name):
 
 SIZES = {"1.5b": _preset("qwen2.5-1.5b"), "7b": _preset("qwen2.5-7b"), "14b": _preset("qwen2.5-14b")}
 # Other designs at the same layer sizes (width, heads, feed-forward), for --design.
-DESIGNS = {"ruvenex": {"1.5b": "ruvenex-1.5b", "7b": "ruvenex-7b"}, "fozerax": {"1.5b": "fozerax-1.5b", "7b": "fozerax-7b"}}
+DESIGNS = {"ruvenex": {"1.5b": "ruvenex-1.5b", "7b": "ruvenex-7b"}, "fozerax": {"1.5b": "fozerax-1.5b", "7b": "fozerax-7b"},
+           "pefazen": {"1.5b": "pefazen-1.5b", "7b": "pefazen-7b"}}
 # the designs a design is measured beside, besides Qwen2: the closest one the engine has
-BESIDE = {"fozerax": ["ruvenex"]}
+BESIDE = {"fozerax": ["ruvenex"], "pefazen": ["fozerax"]}
 CONFIG = SIZES["1.5b"]
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
@@ -137,7 +139,8 @@ def fill_contexts(eng, batch, context):
     import torch
     for g in eng.cache.groups:
         g.k.normal_(0, 0.5)
-        g.v.normal_(0, 0.5)
+        if g.v is not None:
+            g.v.normal_(0, 0.5)
     for r in range(batch):
         eng.add_request(r)
         assert eng.cache.reserve(r, context)
@@ -392,11 +395,33 @@ def fozerax_flops(cfg, T):
     return total + 2 * W * cfg["vocab"]
 
 
+def pefazen_flops(cfg, T):
+    """Arithmetic of a prompt of T tokens through a Pefazen configuration as the design states it: the projections,
+    per-head keys and values from the latents, scores over head_dim + rot_dim and sums over vdim within the window,
+    and the chosen experts only (what an engine spends beyond that is its own)."""
+    W, total = cfg["width"], 0.0
+    for l in cfg["layers"]:
+        m = l["mixer"]
+        H, d, dr, dv, rq, rkv = (m[k] for k in ("heads", "dim", "rot_dim", "vdim", "q_rank", "kv_rank"))
+        n = W * rq + rq * H * (d + dr) + rkv * H * (d + dv) + H * dv * W + (W * H if l["type"] == "latent_attention" else 0)
+        if m.get("kv_from") is None:
+            n += W * (rkv + dr)
+        total += 2 * T * n
+        win = min(T, (m.get("mask") or {}).get("size") or T)
+        total += 2 * H * (d + dr + dv) * (T * win - win * (win - 1) / 2)
+        f = l["mlp"]
+        if f:
+            total += 2 * T * W * (2 * f["router"]["top"] * f["expert"]["ff"] + f["router"]["experts"])
+    return total + 2 * W * cfg["vocab"]
+
+
 def design_flops(cfg, T):
     """Arithmetic of a prompt of T tokens through a model of --design's configuration (matrix products, attention
     scores and sums, the recurrence's state updates and read-outs), logits at the last place only."""
     if cfg.get("architecture") == "Fozerax":
         return fozerax_flops(cfg, T)
+    if cfg.get("architecture") == "Pefazen":
+        return pefazen_flops(cfg, T)
     W, total = cfg["width"], 0.0
     for l in cfg["layers"]:
         a, r = l["mixer"]["left"], l["mixer"]["right"]

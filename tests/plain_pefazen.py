@@ -229,4 +229,15 @@ def forward(cfg: Mapping, W: Mapping[str, torch.Tensor], ids: Sequence[int], lay
         if layers_out is not None:
             layers_out.append(x.clone())
     h = _rnd(layer_norm(x, W["final.norm"], eps))
-    return soft_cap(linear(h, W["head"]) * float(cfg["logit_scale"]), float(cfg["logit_softcap"]))
+    logits = linear(h, W["head"]) * float(cfg.get("logit_scale", 1.0))
+    return soft_cap(logits, float(cfg["logit_softcap"])) if cfg.get("logit_softcap") else logits
+
+
+def greedy(cfg: Mapping, W: Mapping[str, torch.Tensor], prompt: Sequence[int], n_new: int) -> List[int]:
+    """n_new tokens, each the first index of the largest logit after the whole sequence so far."""
+    ids, out = list(prompt), []
+    for _ in range(n_new):
+        tok = int(torch.argmax(forward(cfg, W, ids)[-1]))
+        ids.append(tok)
+        out.append(tok)
+    return out
