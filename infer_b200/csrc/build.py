@@ -32,6 +32,7 @@ MODULES: Dict[str, str] = {
     "seq": "seq_ops.cu",         # filters over time, pair rotation, gated recurrence, side-by-side sublayers
     "mix": "mix_ops.cu",         # norms on sublayer results, decayed and delta-rule recurrences, routers, row norms of q and k
     "latent": "latent_ops.cu",   # attention through low-rank latents, layer norm, sigmoid router, capped logits
+    "latent_pf": "latent_prefill.cu",   # the same attention for prompt portions: per-head keys and values, tensor cores
     "gemvb": "gemv_bulk.cu",
     "gemm": "gemm_tcgen05.cu",
     "attn": "attention_fast.cu",
@@ -40,7 +41,7 @@ MODULES: Dict[str, str] = {
 }
 HEADERS = ["common.cuh", "gemm_static.h", "tma_map.cuh"]
 # modules that are compiled per model size: the variant that build_all() makes (others are built at first use)
-DEFAULT_DEFINES = {"attn": {"IB_HEAD_DIM": 128}, "attn_tc": {"IB_HEAD_DIM": 128}}
+DEFAULT_DEFINES = {"attn": {"IB_HEAD_DIM": 128}, "attn_tc": {"IB_HEAD_DIM": 128}, "latent_pf": {"IB_QK_DIM": 192, "IB_V_DIM": 128}}
 
 
 class BuildError(RuntimeError):

@@ -128,47 +128,136 @@ latent_prepare_kernel(const float* __restrict__ rows, int64_t ld, int q_col, int
 }
 
 // ------------------------------------------------------------------------------------------------
-// Queries in the latent space. q [T][H][d + dr] (a head's unrotated channels, then its rotated ones); w_uk [H][d][R]
-// (the key up-projection as checkpoints store it, [H * d, R]); out [T][H][R + dr]:
-//   out[t, h, r] = sum_e q[t, h, e] * w_uk[h, e, r] (e ascending),  out[t, h, R:] = rotate(q[t, h, d:], position).
-// One CTA per (LQ_TOK tokens, head, 128 latent channels): a weight is read once for LQ_TOK tokens.
-constexpr int LQ_TOK = 8, LQ_THREADS = 128;
+// Products of a step's rows with one small matrix per head: out[t, h, n] = sum_k a[t, h, k] * B[h][k][n], B row-major
+// with n contiguous. One CTA of 256 threads per (HP_TOK tokens, head, tile of 16 * C columns), C = 16 bytes of T per
+// thread. A thread owns C neighbouring columns of every token and every 16th k (k = slice, slice + 16, ...), so a
+// matrix row is read once, by 16-byte loads, for all HP_TOK tokens; the 16 slice sums of a column are added in slice
+// order (pairs by a shuffle, then the eight warps in order through shared memory). The order of a sum depends on k
+// alone: a token's result does not depend on which other tokens share its CTA. Leaves the eight warps' partial sums
+// in `red` [8][HP_TOK][16 * C] behind a barrier.
+// With `seg_start` the CTAs serve the tokens of one-token segments only: rows of longer segments are neither read nor
+// written (their attention runs elsewhere).
+constexpr int HP_TOK = 8, HP_THREADS = 256, HP_CL = 16, HP_KS = HP_THREADS / HP_CL, HP_WARPS = HP_THREADS / 32;
 
 template <typename T>
-__global__ void __launch_bounds__(LQ_THREADS)
-latent_query_kernel(const T* __restrict__ q, const T* __restrict__ w_uk, const float* __restrict__ cos_t,
-                    const float* __restrict__ sin_t, int layout, int n_rot, const int* __restrict__ positions,
-                    T* __restrict__ out, int64_t n_tokens, int n_heads, int d, int dr, int R) {
-    ib::pdl_wait();
-    extern __shared__ float lq_q[];                   // [LQ_TOK][d]
-    const int64_t t0 = int64_t(blockIdx.x) * LQ_TOK;
-    const int h = blockIdx.y, tid = threadIdx.x;
-    const int nt = int(min(int64_t(LQ_TOK), n_tokens - t0));
-    for (int i = tid; i < LQ_TOK * d; i += LQ_THREADS) {
-        const int tt = i / d, e = i - tt * d;
-        lq_q[i] = tt < nt ? ib::to_f32(q[((t0 + tt) * n_heads + h) * (d + dr) + e]) : 0.0f;
+struct HpCols { static constexpr int v = 16 / int(sizeof(T)); };
+
+template <typename T>
+__device__ __forceinline__ void load_cols(const T* p, float (&x)[HpCols<T>::v]);
+template <>
+__device__ __forceinline__ void load_cols<float>(const float* p, float (&x)[4]) {
+    const float4 a = *reinterpret_cast<const float4*>(p);
+    x[0] = a.x; x[1] = a.y; x[2] = a.z; x[3] = a.w;
+}
+template <>
+__device__ __forceinline__ void load_cols<bf16>(const bf16* p, float (&x)[8]) {
+    const uint4 u = *reinterpret_cast<const uint4*>(p);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const float2 f = __bfloat1622float2(h[i]);
+        x[2 * i] = f.x;
+        x[2 * i + 1] = f.y;
+    }
+}
+
+template <typename T>
+__device__ __forceinline__ void head_product_tile(const float* __restrict__ a_s, const T* __restrict__ B, int K, int N, int n0,
+                                                  bool vec, float* __restrict__ red) {
+    constexpr int C = HpCols<T>::v, NT = HP_CL * C;
+    const int tid = threadIdx.x, cl = tid % HP_CL, ks = tid / HP_CL, warp = tid >> 5, lane = tid & 31;
+    const int nb = n0 + cl * C;
+    float acc[HP_TOK][C];
+#pragma unroll
+    for (int tt = 0; tt < HP_TOK; tt++)
+#pragma unroll
+        for (int c = 0; c < C; c++) acc[tt][c] = 0.0f;
+    if (nb < N) {
+#pragma unroll 4
+        for (int k = ks; k < K; k += HP_KS) {
+            float w[C];
+            const T* src = B + int64_t(k) * N + nb;
+            if (vec) {
+                load_cols<T>(src, w);
+            } else {
+#pragma unroll
+                for (int c = 0; c < C; c++) w[c] = nb + c < N ? ib::to_f32(src[c]) : 0.0f;
+            }
+#pragma unroll
+            for (int tt = 0; tt < HP_TOK; tt++) {
+                const float a = a_s[tt * K + k];
+#pragma unroll
+                for (int c = 0; c < C; c++) acc[tt][c] = fmaf(a, w[c], acc[tt][c]);
+            }
+        }
+    }
+#pragma unroll
+    for (int tt = 0; tt < HP_TOK; tt++)
+#pragma unroll
+        for (int c = 0; c < C; c++) acc[tt][c] += __shfl_xor_sync(0xffffffffu, acc[tt][c], 16);
+    if (lane < 16) {
+#pragma unroll
+        for (int tt = 0; tt < HP_TOK; tt++)
+#pragma unroll
+            for (int c = 0; c < C; c++) red[(warp * HP_TOK + tt) * NT + cl * C + c] = acc[tt][c];
     }
     __syncthreads();
-    const int r = blockIdx.z * LQ_THREADS + tid;
-    if (r < R) {
-        float acc[LQ_TOK];
-#pragma unroll
-        for (int tt = 0; tt < LQ_TOK; tt++) acc[tt] = 0.0f;
-        const T* w = w_uk + int64_t(h) * d * R + r;
-#pragma unroll 4
-        for (int e = 0; e < d; e++) {
-            const float wv = ib::to_f32(w[int64_t(e) * R]);
-#pragma unroll
-            for (int tt = 0; tt < LQ_TOK; tt++) acc[tt] = fmaf(lq_q[tt * d + e], wv, acc[tt]);
+}
+
+// bit tt of the result: token t0 + tt exists and (without seg_start) counts, or lies in a one-token segment
+__device__ __forceinline__ unsigned tokens_served(int64_t t0, int nt, const int* __restrict__ token_seg, const int* __restrict__ seg_start) {
+    unsigned mask = 0;
+    for (int tt = 0; tt < nt; tt++) {
+        bool on = true;
+        if (seg_start) {
+            const int sg = token_seg[t0 + tt];
+            on = seg_start[sg + 1] - seg_start[sg] == 1;
         }
+        mask |= on ? 1u << tt : 0u;
+    }
+    return mask;
+}
+
+// ------------------------------------------------------------------------------------------------
+// Queries in the latent space. q [T][H][d + dr] (a head's unrotated channels, then its rotated ones); w_uk [H][d][R]
+// (the key up-projection as checkpoints store it, [H * d, R]); out [T][H][R + dr]:
+//   out[t, h, r] = sum_e q[t, h, e] * w_uk[h, e, r],  out[t, h, R:] = rotate(q[t, h, d:], position).
+template <typename T>
+__global__ void __launch_bounds__(HP_THREADS)
+latent_query_kernel(const T* __restrict__ q, const T* __restrict__ w_uk, const float* __restrict__ cos_t,
+                    const float* __restrict__ sin_t, int layout, int n_rot, const int* __restrict__ positions,
+                    T* __restrict__ out, int64_t n_tokens, int n_heads, int d, int dr, int R, int vec,
+                    const int* __restrict__ token_seg, const int* __restrict__ seg_start) {
+    ib::pdl_wait();
+    constexpr int NT = HP_CL * HpCols<T>::v;
+    extern __shared__ __align__(16) float hp_sm[];
+    float* a_s = hp_sm;                               // [HP_TOK][d]
+    float* red = a_s + HP_TOK * d;                    // [HP_WARPS][HP_TOK][NT]
+    const int64_t t0 = int64_t(blockIdx.x) * HP_TOK;
+    const int h = blockIdx.y, tid = threadIdx.x;
+    const int nt = int(min(int64_t(HP_TOK), n_tokens - t0));
+    const unsigned served = tokens_served(t0, nt, token_seg, seg_start);
+    if (!served) return;
+    for (int i = tid; i < HP_TOK * d; i += HP_THREADS) {
+        const int tt = i / d, e = i - tt * d;
+        a_s[i] = (served >> tt & 1u) ? ib::to_f32(q[((t0 + tt) * n_heads + h) * (d + dr) + e]) : 0.0f;
+    }
+    __syncthreads();
+    const int n0 = blockIdx.z * NT;
+    head_product_tile<T>(a_s, w_uk + int64_t(h) * d * R, d, R, n0, vec != 0, red);
+    for (int i = tid; i < HP_TOK * NT; i += HP_THREADS) {
+        const int tt = i / NT, n = n0 + (i - tt * NT);
+        if (!(served >> tt & 1u) || n >= R) continue;
+        float s = 0.0f;
 #pragma unroll
-        for (int tt = 0; tt < LQ_TOK; tt++)
-            if (tt < nt) out[((t0 + tt) * n_heads + h) * (R + dr) + r] = ib::from_f32<T>(acc[tt]);
+        for (int w = 0; w < HP_WARPS; w++) s += red[(w * HP_TOK + tt) * NT + (n - n0)];
+        out[((t0 + tt) * n_heads + h) * (R + dr) + n] = ib::from_f32<T>(s);
     }
     if (blockIdx.z == 0) {
         const int half = n_rot / 2;
-        for (int i = tid; i < nt * half; i += LQ_THREADS) {
+        for (int i = tid; i < nt * half; i += HP_THREADS) {
             const int tt = i / half, j = i - tt * half;
+            if (!(served >> tt & 1u)) continue;
             const int64_t t = t0 + tt;
             const int pos = positions[t];
             const int a = layout == 0 ? 2 * j : j, b = layout == 0 ? 2 * j + 1 : j + half;
@@ -180,8 +269,9 @@ latent_query_kernel(const T* __restrict__ q, const T* __restrict__ w_uk, const f
             dst[b] = ib::from_f32<T>(v * c + u * sn);
         }
         const int rest = dr - n_rot;
-        for (int i = tid; i < nt * rest; i += LQ_THREADS) {
+        for (int i = tid; i < nt * rest; i += HP_THREADS) {
             const int tt = i / rest, j = n_rot + (i - tt * rest);
+            if (!(served >> tt & 1u)) continue;
             const int64_t t = t0 + tt;
             out[(t * n_heads + h) * (R + dr) + R + j] = q[(t * n_heads + h) * (d + dr) + d + j];
         }
@@ -225,6 +315,7 @@ __device__ __forceinline__ void load8<bf16>(const bf16* p, float (&x)[8]) {
 }
 
 // GB: heads of a CTA rounded up to 1, 2, 4 or 8; NC: channel passes of a thread (dv <= NC * KC).
+// With `seg_start`, tokens of segments longer than one token are left out (their attention runs elsewhere).
 // n_splits 1: the CTA walks all chunks of its token and writes the context. n_splits > 1 (steps of single tokens):
 // CTA z takes chunk z of its token and leaves (m, l, o) in `parts` [token][head][split][2 + dv].
 template <typename T, int GB, int NC>
@@ -232,10 +323,15 @@ __global__ void __launch_bounds__(KC)
 latent_attention_kernel(const T* __restrict__ q, const T* __restrict__ cache, const int* __restrict__ block_table,
                         int64_t max_blocks, const int* __restrict__ token_seg, const int* __restrict__ positions,
                         T* __restrict__ out, float* __restrict__ parts, int n_heads, int group, int dk, int dv, int page_size,
-                        int window, float scale, int64_t n_pages, int n_splits, int vec, int vec_v, int* status) {
+                        int window, float scale, int64_t n_pages, int n_splits, int vec, int vec_v, int* status,
+                        const int* __restrict__ seg_start) {
     ib::pdl_wait();
     const int64_t t = blockIdx.x;
     const int g = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    if (seg_start) {                                     // tokens of one-token segments only
+        const int sg = token_seg[t];
+        if (seg_start[sg + 1] - seg_start[sg] != 1) return;
+    }
     const int pos = positions[t];
     const int lo = window > 0 ? max(0, pos - window + 1) : 0;
     const int c_lo = lo / KC, c_hi = pos / KC;
@@ -401,25 +497,44 @@ latent_attention_kernel(const T* __restrict__ q, const T* __restrict__ cache, co
     }
 }
 
-// One warp per (token, head): the chunks' parts merged in ascending order, then the division.
+// One CTA per (token, head), one thread per channel: the chunks' parts merged in ascending order, then the division.
+// The chunks' maxima and sums wait in shared memory; every thread walks the same chain over them, and its own loads
+// of the parts' channels do not depend on the chain, so they are in flight together.
+constexpr int MG_THREADS = 128, MG_STAGE = 256;
+
 template <typename T>
-__global__ void latent_attention_merge_kernel(const float* __restrict__ parts, const int* __restrict__ positions,
-                                              T* __restrict__ out, int64_t n_rows, int n_heads, int dv, int window, int n_splits) {
+__global__ void __launch_bounds__(MG_THREADS)
+latent_attention_merge_kernel(const float* __restrict__ parts, const int* __restrict__ positions, T* __restrict__ out,
+                              int n_heads, int dv, int window, int n_splits, const int* __restrict__ token_seg,
+                              const int* __restrict__ seg_start) {
     ib::pdl_wait();
-    const int lane = threadIdx.x & 31;
-    const int64_t r = int64_t(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    if (r >= n_rows) return;
-    const int pos = positions[r / n_heads];
+    __shared__ float ml_s[2 * MG_STAGE];
+    const int64_t r = blockIdx.x;
+    const int64_t t = r / n_heads;
+    if (seg_start) {
+        const int sg = token_seg[t];
+        if (seg_start[sg + 1] - seg_start[sg] != 1) return;
+    }
+    const int pos = positions[t];
     const int lo = window > 0 ? max(0, pos - window + 1) : 0;
     const int n = min(n_splits, pos / KC - lo / KC + 1);
-    const float* mine = parts + r * n_splits * int64_t(dv + 2);
-    for (int c = lane; c < dv; c += 32) {
+    const int stride = dv + 2;
+    const float* mine = parts + r * n_splits * int64_t(stride);
+    const bool staged = n <= MG_STAGE;
+    if (staged) {
+        for (int i = threadIdx.x; i < 2 * n; i += MG_THREADS) ml_s[i] = mine[(i >> 1) * int64_t(stride) + (i & 1)];
+        __syncthreads();
+    }
+    for (int c = threadIdx.x; c < dv; c += MG_THREADS) {
         float M = -INFINITY, L = 0.0f, O = 0.0f;
+#pragma unroll 8
         for (int i = 0; i < n; i++) {
-            const float* p = mine + i * int64_t(dv + 2);
+            const float* p = mine + i * int64_t(stride);
+            const float v = p[2 + c];
+            const float m = staged ? ml_s[2 * i] : p[0], l = staged ? ml_s[2 * i + 1] : p[1];
             float a, b;
-            merge_state(M, L, p[0], p[1], a, b);
-            O = merge_value(O, a, p[2 + c], b);
+            merge_state(M, L, m, l, a, b);
+            O = merge_value(O, a, v, b);
         }
         out[r * dv + c] = ib::from_f32<T>(O * (L > 0.0f ? 1.0f / L : 0.0f));
     }
@@ -428,54 +543,39 @@ __global__ void latent_attention_merge_kernel(const float* __restrict__ parts, c
 // ------------------------------------------------------------------------------------------------
 // A head's value up-projection on its latent context, the head's gate and a constant:
 //   out[t, h * dv + e] = mult * sigmoid(gates[t, gate_col + h]) * sum_r ctx[t, h, r] * w_uvT[h, r, e]
-// (gate_col < 0: no gate). w_uvT is the up-projection transposed per head, so that neighbouring threads read
-// neighbouring values. One CTA per (LO_TOK tokens, head); its 128 threads are ev channels x 128 / ev slices of r
-// (ev a power of two >= dv, at most 128); slice sums are added in slice order.
-constexpr int LO_TOK = 8, LO_THREADS = 128;
-
+// (gate_col < 0: no gate). w_uvT is the up-projection transposed per head, so that the columns of a row are
+// neighbours (head_product_tile above).
 template <typename T>
-__global__ void __launch_bounds__(LO_THREADS)
+__global__ void __launch_bounds__(HP_THREADS)
 latent_output_kernel(const T* __restrict__ ctx, const T* __restrict__ w_uvT, const float* __restrict__ gates, int64_t gate_ld,
-                     int gate_col, float mult, T* __restrict__ out, int64_t n_tokens, int n_heads, int R, int dv, int ev) {
+                     int gate_col, float mult, T* __restrict__ out, int64_t n_tokens, int n_heads, int R, int dv, int vec,
+                     const int* __restrict__ token_seg, const int* __restrict__ seg_start) {
     ib::pdl_wait();
-    extern __shared__ float lo_sm[];
-    float* cs = lo_sm;                                // [LO_TOK][R]
-    float* red = cs + LO_TOK * R;                     // [slices][LO_TOK][ev]
-    const int64_t t0 = int64_t(blockIdx.x) * LO_TOK;
+    constexpr int NT = HP_CL * HpCols<T>::v;
+    extern __shared__ __align__(16) float hp_sm[];
+    float* a_s = hp_sm;                               // [HP_TOK][R]
+    float* red = a_s + HP_TOK * R;                    // [HP_WARPS][HP_TOK][NT]
+    const int64_t t0 = int64_t(blockIdx.x) * HP_TOK;
     const int h = blockIdx.y, tid = threadIdx.x;
-    const int nt = int(min(int64_t(LO_TOK), n_tokens - t0));
-    for (int i = tid; i < LO_TOK * R; i += LO_THREADS) {
+    const int nt = int(min(int64_t(HP_TOK), n_tokens - t0));
+    const unsigned served = tokens_served(t0, nt, token_seg, seg_start);
+    if (!served) return;
+    for (int i = tid; i < HP_TOK * R; i += HP_THREADS) {
         const int tt = i / R, r = i - tt * R;
-        cs[i] = tt < nt ? ib::to_f32(ctx[((t0 + tt) * n_heads + h) * R + r]) : 0.0f;
+        a_s[i] = (served >> tt & 1u) ? ib::to_f32(ctx[((t0 + tt) * n_heads + h) * R + r]) : 0.0f;
     }
     __syncthreads();
-    const int slices = LO_THREADS / ev, e = tid % ev, sl = tid / ev;
-    for (int e0 = 0; e0 < dv; e0 += ev) {
-        const int ee = e0 + e;
-        float acc[LO_TOK];
+    const int n0 = blockIdx.z * NT;
+    head_product_tile<T>(a_s, w_uvT + int64_t(h) * R * dv, R, dv, n0, vec != 0, red);
+    for (int i = tid; i < HP_TOK * NT; i += HP_THREADS) {
+        const int tt = i / NT, n = n0 + (i - tt * NT);
+        if (!(served >> tt & 1u) || n >= dv) continue;
+        float s = 0.0f;
 #pragma unroll
-        for (int tt = 0; tt < LO_TOK; tt++) acc[tt] = 0.0f;
-        if (ee < dv) {
-            const T* w = w_uvT + int64_t(h) * R * dv + ee;
-            for (int r = sl; r < R; r += slices) {
-                const float wv = ib::to_f32(w[int64_t(r) * dv]);
-#pragma unroll
-                for (int tt = 0; tt < LO_TOK; tt++) acc[tt] = fmaf(cs[tt * R + r], wv, acc[tt]);
-            }
-        }
-#pragma unroll
-        for (int tt = 0; tt < LO_TOK; tt++) red[(sl * LO_TOK + tt) * ev + e] = acc[tt];
-        __syncthreads();
-        if (sl == 0 && ee < dv) {
-            for (int tt = 0; tt < nt; tt++) {
-                float s = 0.0f;
-                for (int k = 0; k < slices; k++) s += red[(k * LO_TOK + tt) * ev + e];
-                const int64_t t = t0 + tt;
-                const float gate = gate_col >= 0 ? sigmoid_(gates[t * gate_ld + gate_col + h]) : 1.0f;
-                out[(t * n_heads + h) * dv + ee] = ib::from_f32<T>(s * gate * mult);
-            }
-        }
-        __syncthreads();
+        for (int w = 0; w < HP_WARPS; w++) s += red[(w * HP_TOK + tt) * NT + (n - n0)];
+        const int64_t t = t0 + tt;
+        const float gate = gate_col >= 0 ? sigmoid_(gates[t * gate_ld + gate_col + h]) : 1.0f;
+        out[(t * n_heads + h) * dv + n] = ib::from_f32<T>(s * gate * mult);
     }
 }
 
@@ -613,22 +713,36 @@ IB_EXPORT int ib_latent_prepare(const float* rows, int64_t ld, int q_col, int q_
     return ib::check_launch("ib_latent_prepare");
 }
 
+namespace {
+template <typename T>
+size_t head_product_smem(int K) { return (size_t(HP_TOK) * K + size_t(HP_WARPS) * HP_TOK * HP_CL * HpCols<T>::v) * sizeof(float); }
+}  // namespace
+
+// `single_start` (the step's seg_start, or null): only tokens that are a segment of their own are served.
 IB_EXPORT int ib_latent_query(const void* q, const void* w_uk, const float* cos_t, const float* sin_t, int layout, int n_rot,
                               const int* positions, void* out, int64_t n_tokens, int n_heads, int d, int dr, int R, int dtype,
-                              cudaStream_t stream) {
+                              const int* token_seg, const int* single_start, cudaStream_t stream) {
     if (n_tokens <= 0) return IB_OK;
     if (n_heads <= 0 || n_heads > 65535 || d <= 0 || dr < 0 || R <= 0 || n_rot < 0 || n_rot % 2 || n_rot > dr)
         return ib::fail(IB_ERR_ARG, "ib_latent_query: sizes heads %d, %d + %d channels, rank %d, %d rotated", n_heads, d, dr, R, n_rot);
-    const size_t smem = size_t(LQ_TOK) * d * sizeof(float);
-    if (smem > 48 * 1024) return ib::fail(IB_ERR_ARG, "ib_latent_query: heads of %d unrotated channels are too long", d);
-    const dim3 grid{blocks_for(n_tokens, LQ_TOK), unsigned(n_heads), blocks_for(R, LQ_THREADS)};
-    if (dtype == IB_F32)
-        IB_LAUNCH(latent_query_kernel<float>, grid, LQ_THREADS, smem, (const float*)q, (const float*)w_uk, cos_t, sin_t, layout, n_rot,
-                  positions, (float*)out, n_tokens, n_heads, d, dr, R);
-    else if (dtype == IB_BF16)
-        IB_LAUNCH(latent_query_kernel<bf16>, grid, LQ_THREADS, smem, (const bf16*)q, (const bf16*)w_uk, cos_t, sin_t, layout, n_rot,
-                  positions, (bf16*)out, n_tokens, n_heads, d, dr, R);
-    else
+    if (single_start && !token_seg) return ib::fail(IB_ERR_ARG, "ib_latent_query: serving single tokens needs token_seg");
+    if (dtype == IB_F32) {
+        constexpr int NT = HP_CL * HpCols<float>::v;
+        const size_t smem = head_product_smem<float>(d);
+        const int rc = allow_smem(latent_query_kernel<float>, smem);
+        if (rc) return rc;
+        const dim3 grid{blocks_for(n_tokens, HP_TOK), unsigned(n_heads), blocks_for(R, NT)};
+        IB_LAUNCH(latent_query_kernel<float>, grid, HP_THREADS, smem, (const float*)q, (const float*)w_uk, cos_t, sin_t, layout, n_rot,
+                  positions, (float*)out, n_tokens, n_heads, d, dr, R, int(R % HpCols<float>::v == 0), token_seg, single_start);
+    } else if (dtype == IB_BF16) {
+        constexpr int NT = HP_CL * HpCols<bf16>::v;
+        const size_t smem = head_product_smem<bf16>(d);
+        const int rc = allow_smem(latent_query_kernel<bf16>, smem);
+        if (rc) return rc;
+        const dim3 grid{blocks_for(n_tokens, HP_TOK), unsigned(n_heads), blocks_for(R, NT)};
+        IB_LAUNCH(latent_query_kernel<bf16>, grid, HP_THREADS, smem, (const bf16*)q, (const bf16*)w_uk, cos_t, sin_t, layout, n_rot,
+                  positions, (bf16*)out, n_tokens, n_heads, d, dr, R, int(R % HpCols<bf16>::v == 0), token_seg, single_start);
+    } else
         return ib::fail(IB_ERR_ARG, "ib_latent_query: unknown dtype %d", dtype);
     return ib::check_launch("ib_latent_query");
 }
@@ -643,7 +757,8 @@ namespace {
 template <typename T, int GB, int NC>
 int launch_latent_attention(const void* q, const void* cache, const int* block_table, int64_t max_blocks, const int* token_seg,
                             const int* positions, void* out, float* parts, int64_t n_tokens, int n_heads, int group, int dk, int dv,
-                            int page_size, int window, float scale, int64_t n_pages, int n_splits, int* status, cudaStream_t stream) {
+                            int page_size, int window, float scale, int64_t n_pages, int n_splits, int* status, const int* single_start,
+                            cudaStream_t stream) {
     const int dq = (dk + 3) & ~3;
     const size_t smem = size_t(GB * dq + GB * KC + 2 * GMAX) * sizeof(float) + KC * sizeof(int64_t) + size_t(VT) * dv * sizeof(T);
     const int rc = allow_smem(latent_attention_kernel<T, GB, NC>, smem);
@@ -651,7 +766,8 @@ int launch_latent_attention(const void* q, const void* cache, const int* block_t
     const int vec = dk % 8 == 0, vec_v = vec && (dv * sizeof(T)) % 16 == 0;
     const dim3 grid{unsigned(n_tokens), unsigned((n_heads + group - 1) / group), unsigned(n_splits)};
     IB_LAUNCH((latent_attention_kernel<T, GB, NC>), grid, KC, smem, (const T*)q, (const T*)cache, block_table, max_blocks, token_seg,
-              positions, (T*)out, parts, n_heads, group, dk, dv, page_size, window, scale, n_pages, n_splits, vec, vec_v, status);
+              positions, (T*)out, parts, n_heads, group, dk, dv, page_size, window, scale, n_pages, n_splits, vec, vec_v, status,
+              single_start);
     return IB_OK;
 }
 
@@ -659,11 +775,11 @@ template <typename T>
 int pick_latent_attention(int gb, int nc, const void* q, const void* cache, const int* block_table, int64_t max_blocks,
                           const int* token_seg, const int* positions, void* out, float* parts, int64_t n_tokens, int n_heads, int group,
                           int dk, int dv, int page_size, int window, float scale, int64_t n_pages, int n_splits, int* status,
-                          cudaStream_t stream) {
+                          const int* single_start, cudaStream_t stream) {
 #define IB_LA(GB_, NC_)                                                                                                      \
     if (gb == GB_ && nc == NC_)                                                                                              \
         return launch_latent_attention<T, GB_, NC_>(q, cache, block_table, max_blocks, token_seg, positions, out, parts, n_tokens, \
-                                                    n_heads, group, dk, dv, page_size, window, scale, n_pages, n_splits, status, stream);
+                                                    n_heads, group, dk, dv, page_size, window, scale, n_pages, n_splits, status, single_start, stream);
     IB_LA(1, 1) IB_LA(1, 2) IB_LA(1, 4) IB_LA(2, 1) IB_LA(2, 2) IB_LA(2, 4) IB_LA(4, 1) IB_LA(4, 2) IB_LA(4, 4) IB_LA(8, 1) IB_LA(8, 2) IB_LA(8, 4)
 #undef IB_LA
     return ib::fail(IB_ERR_ARG, "ib_latent_attention: no kernel for groups of %d heads and %d channel passes", gb, nc);
@@ -676,7 +792,7 @@ int pick_latent_attention(int gb, int nc, const void* q, const void* cache, cons
 IB_EXPORT int ib_latent_attention(const void* q, const void* cache, const int* block_table, int64_t max_blocks, const int* token_seg,
                                   const int* positions, void* out, float* parts, int64_t n_tokens, int n_heads, int dk, int dv,
                                   int page_size, int window, float scale, int64_t n_pages, int n_splits, int dtype, int* status,
-                                  cudaStream_t stream) {
+                                  const int* single_start, cudaStream_t stream) {
     if (n_tokens <= 0) return IB_OK;
     if (n_heads <= 0 || dk <= 0 || dk > 1024 || dv <= 0 || dv > dk || dv > 4 * KC)
         return ib::fail(IB_ERR_ARG, "ib_latent_attention: %d heads, rows of %d with values of %d are outside what the kernel takes", n_heads, dk, dv);
@@ -688,41 +804,49 @@ IB_EXPORT int ib_latent_attention(const void* q, const void* cache, const int* b
     int rc;
     if (dtype == IB_F32)
         rc = pick_latent_attention<float>(gb, nc, q, cache, block_table, max_blocks, token_seg, positions, out, parts, n_tokens, n_heads,
-                                          group, dk, dv, page_size, window, scale, n_pages, n_splits, status, stream);
+                                          group, dk, dv, page_size, window, scale, n_pages, n_splits, status, single_start, stream);
     else if (dtype == IB_BF16)
         rc = pick_latent_attention<bf16>(gb, nc, q, cache, block_table, max_blocks, token_seg, positions, out, parts, n_tokens, n_heads,
-                                         group, dk, dv, page_size, window, scale, n_pages, n_splits, status, stream);
+                                         group, dk, dv, page_size, window, scale, n_pages, n_splits, status, single_start, stream);
     else
         return ib::fail(IB_ERR_ARG, "ib_latent_attention: unknown dtype %d", dtype);
     if (rc) return rc;
     if (n_splits > 1) {
         const int64_t n_rows = n_tokens * n_heads;
+        if (n_rows > 0x7fffffff) return ib::fail(IB_ERR_ARG, "ib_latent_attention: too many rows to merge");
         if (dtype == IB_F32)
-            IB_LAUNCH(latent_attention_merge_kernel<float>, blocks_for(n_rows, 4), 128, 0, parts, positions, (float*)out, n_rows, n_heads, dv,
-                      window, n_splits);
+            IB_LAUNCH(latent_attention_merge_kernel<float>, unsigned(n_rows), MG_THREADS, 0, parts, positions, (float*)out, n_heads, dv,
+                      window, n_splits, token_seg, single_start);
         else
-            IB_LAUNCH(latent_attention_merge_kernel<bf16>, blocks_for(n_rows, 4), 128, 0, parts, positions, (bf16*)out, n_rows, n_heads, dv,
-                      window, n_splits);
+            IB_LAUNCH(latent_attention_merge_kernel<bf16>, unsigned(n_rows), MG_THREADS, 0, parts, positions, (bf16*)out, n_heads, dv,
+                      window, n_splits, token_seg, single_start);
     }
     return ib::check_launch("ib_latent_attention");
 }
 
 IB_EXPORT int ib_latent_output(const void* ctx, const void* w_uvT, const float* gates, int64_t gate_ld, int gate_col, float mult,
-                               void* out, int64_t n_tokens, int n_heads, int R, int dv, int dtype, cudaStream_t stream) {
+                               void* out, int64_t n_tokens, int n_heads, int R, int dv, int dtype, const int* token_seg,
+                               const int* single_start, cudaStream_t stream) {
     if (n_tokens <= 0) return IB_OK;
     if (n_heads <= 0 || n_heads > 65535 || R <= 0 || dv <= 0) return ib::fail(IB_ERR_ARG, "ib_latent_output: sizes %d heads, rank %d, values %d", n_heads, R, dv);
-    int ev = 1;
-    while (ev < dv && ev < LO_THREADS) ev *= 2;
-    const size_t smem = size_t(LO_TOK) * R * sizeof(float) + size_t(LO_THREADS) * LO_TOK * sizeof(float);
-    if (smem > 48 * 1024) return ib::fail(IB_ERR_ARG, "ib_latent_output: a rank of %d is too large", R);
-    const dim3 grid{blocks_for(n_tokens, LO_TOK), unsigned(n_heads), 1u};
-    if (dtype == IB_F32)
-        IB_LAUNCH(latent_output_kernel<float>, grid, LO_THREADS, smem, (const float*)ctx, (const float*)w_uvT, gates, gate_ld, gate_col, mult,
-                  (float*)out, n_tokens, n_heads, R, dv, ev);
-    else if (dtype == IB_BF16)
-        IB_LAUNCH(latent_output_kernel<bf16>, grid, LO_THREADS, smem, (const bf16*)ctx, (const bf16*)w_uvT, gates, gate_ld, gate_col, mult,
-                  (bf16*)out, n_tokens, n_heads, R, dv, ev);
-    else
+    if (single_start && !token_seg) return ib::fail(IB_ERR_ARG, "ib_latent_output: serving single tokens needs token_seg");
+    if (dtype == IB_F32) {
+        constexpr int NT = HP_CL * HpCols<float>::v;
+        const size_t smem = head_product_smem<float>(R);
+        const int rc = allow_smem(latent_output_kernel<float>, smem);
+        if (rc) return rc;
+        const dim3 grid{blocks_for(n_tokens, HP_TOK), unsigned(n_heads), blocks_for(dv, NT)};
+        IB_LAUNCH(latent_output_kernel<float>, grid, HP_THREADS, smem, (const float*)ctx, (const float*)w_uvT, gates, gate_ld, gate_col, mult,
+                  (float*)out, n_tokens, n_heads, R, dv, int(dv % HpCols<float>::v == 0), token_seg, single_start);
+    } else if (dtype == IB_BF16) {
+        constexpr int NT = HP_CL * HpCols<bf16>::v;
+        const size_t smem = head_product_smem<bf16>(R);
+        const int rc = allow_smem(latent_output_kernel<bf16>, smem);
+        if (rc) return rc;
+        const dim3 grid{blocks_for(n_tokens, HP_TOK), unsigned(n_heads), blocks_for(dv, NT)};
+        IB_LAUNCH(latent_output_kernel<bf16>, grid, HP_THREADS, smem, (const bf16*)ctx, (const bf16*)w_uvT, gates, gate_ld, gate_col, mult,
+                  (bf16*)out, n_tokens, n_heads, R, dv, int(dv % HpCols<bf16>::v == 0), token_seg, single_start);
+    } else
         return ib::fail(IB_ERR_ARG, "ib_latent_output: unknown dtype %d", dtype);
     return ib::check_launch("ib_latent_output");
 }

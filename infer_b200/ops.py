@@ -840,9 +840,10 @@ def latent_prepare(rows: torch.Tensor, q_col: int, q_rank: int, kv_col: int, kv_
 
 
 def latent_query(q: torch.Tensor, w_uk: torch.Tensor, cos: Optional[torch.Tensor], sin: Optional[torch.Tensor], layout: str,
-                 positions: torch.Tensor, n_heads: int, d: int, dr: int) -> torch.Tensor:
+                 positions: torch.Tensor, n_heads: int, d: int, dr: int, single_step=None) -> torch.Tensor:
     """q [T, heads * (d + dr)] and the key up-projection w_uk [heads * d, R] -> queries in the latent space
-    [T, heads, R + dr]: the unrotated channels carried through w_uk, the rotated ones turned by their position."""
+    [T, heads, R + dr]: the unrotated channels carried through w_uk, the rotated ones turned by their position.
+    With ``single_step`` (the step) only the rows of tokens that are a segment of their own are computed."""
     _check(q, "q")
     T = q.shape[0]
     R = w_uk.shape[1]
@@ -855,9 +856,10 @@ def latent_query(q: torch.Tensor, w_uk: torch.Tensor, cos: Optional[torch.Tensor
         _check(sin, "sin", torch.float32, tuple(cos.shape))
     out = torch.empty((T, n_heads, R + dr), dtype=q.dtype, device=q.device)
     f = _fn("latent", "ib_latent_query", [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int64,
-                                          c_int, c_int, c_int, c_int, c_int, c_void_p])
+                                          c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p])
     _call(f, q.data_ptr(), w_uk.data_ptr(), _ptr(cos), _ptr(sin), ROTATION_LAYOUTS[layout], n_rot, positions.data_ptr(), out.data_ptr(),
-          T, n_heads, d, dr, R, dtype_code(q.dtype), _stream())
+          T, n_heads, d, dr, R, dtype_code(q.dtype), single_step.token_seg.data_ptr() if single_step is not None else None,
+          single_step.seg_start.data_ptr() if single_step is not None else None, _stream())
     return out
 
 
@@ -872,10 +874,11 @@ LATENT_CHUNK = 128                 # keys of one chunk of the latent attention k
 
 
 def latent_attention(q: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor, step, dv: int, window: Optional[int],
-                     scale: float, split: Optional[bool] = None) -> torch.Tensor:
+                     scale: float, split: Optional[bool] = None, single_only: bool = False) -> torch.Tensor:
     """q [T, heads, dk] over the rows ``cache`` [pages, page_size, dk] -> contexts [T, heads, dv]: a row's first dv
     channels are its value. ``split``: spread a token's key chunks over CTAs (default: in steps of single tokens that
-    alone would not fill the device); the result's bits do not depend on it."""
+    alone would not fill the device); the result's bits do not depend on it. With ``single_only`` only tokens that are
+    a segment of their own are computed (the other rows of the result are not written)."""
     _check(q, "q")
     T, H, dk = q.shape
     n_pages, page_size, _ = cache.shape
@@ -884,7 +887,8 @@ def latent_attention(q: torch.Tensor, cache: torch.Tensor, block_table: torch.Te
     span = step.max_ctx_len if not window else min(step.max_ctx_len, int(window) + LATENT_CHUNK - 1)
     chunks = max(1, -(-span // LATENT_CHUNK) + (1 if window else 0))
     if split is None:
-        split = step.decode_only and T * ((H + 7) // 8) < 256
+        singles = T if step.decode_only else sum(1 for n in step.seg_lens if n == 1)
+        split = (step.decode_only or single_only) and singles * ((H + 7) // 8) < 256
     n_splits = chunks if (split and chunks > 1) else 1
     out = torch.empty((T, H, dv), dtype=q.dtype, device=q.device)
     parts = None
@@ -892,17 +896,19 @@ def latent_attention(q: torch.Tensor, cache: torch.Tensor, block_table: torch.Te
         from .fast_ops import device_state
         parts = device_state(q.device).workspace(T * H * n_splits * (dv + 2))
     f = _fn("latent", "ib_latent_attention", [c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_int64,
-                                              c_int, c_int, c_int, c_int, c_int, c_float, c_int64, c_int, c_int, c_void_p, c_void_p])
+                                              c_int, c_int, c_int, c_int, c_int, c_float, c_int64, c_int, c_int, c_void_p, c_void_p, c_void_p])
     _call(f, q.data_ptr(), cache.data_ptr(), block_table.data_ptr(), block_table.shape[1], step.token_seg.data_ptr(),
           step.positions.data_ptr(), out.data_ptr(), _ptr(parts), T, H, dk, int(dv), page_size, int(window or 0), float(scale),
-          n_pages, n_splits, dtype_code(q.dtype), _ptr(step.status), _stream())
+          n_pages, n_splits, dtype_code(q.dtype), _ptr(step.status), step.seg_start.data_ptr() if single_only else None, _stream())
     return out
 
 
-def latent_output(ctx: torch.Tensor, w_uvT: torch.Tensor, gates: Optional[torch.Tensor], gate_col: int, mult: float) -> torch.Tensor:
+def latent_output(ctx: torch.Tensor, w_uvT: torch.Tensor, gates: Optional[torch.Tensor], gate_col: int, mult: float,
+                  out: Optional[torch.Tensor] = None, single_step=None) -> torch.Tensor:
     """Latent contexts [T, heads, R] and the value up-projection transposed per head, w_uvT [heads, R, dv] ->
     [T, heads * dv], each head times sigmoid(gates[t, gate_col + head]) (``gates`` float32 rows; None: no gate) and
-    times ``mult``."""
+    times ``mult``. With ``single_step`` (the step) only the rows of tokens that are a segment of their own are
+    written, into ``out`` if given."""
     _check(ctx, "ctx")
     T, H, R = ctx.shape
     dv = w_uvT.shape[2]
@@ -911,11 +917,93 @@ def latent_output(ctx: torch.Tensor, w_uvT: torch.Tensor, gates: Optional[torch.
         _check(gates, "gates", torch.float32)
         if gates.shape[0] != T or gate_col < 0 or gate_col + H > gates.shape[1]:
             raise KernelError("the gates lie outside their rows")
-    out = torch.empty((T, H * dv), dtype=ctx.dtype, device=ctx.device)
+    if out is None:
+        out = torch.empty((T, H * dv), dtype=ctx.dtype, device=ctx.device)
+    else:
+        _check(out, "out", ctx.dtype, (T, H * dv))
     f = _fn("latent", "ib_latent_output", [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_float, c_void_p, c_int64, c_int, c_int, c_int,
-                                           c_int, c_void_p])
+                                           c_int, c_void_p, c_void_p, c_void_p])
     _call(f, ctx.data_ptr(), w_uvT.data_ptr(), _ptr(gates), gates.shape[1] if gates is not None else 0,
-          int(gate_col) if gates is not None else -1, float(mult), out.data_ptr(), T, H, R, dv, dtype_code(ctx.dtype), _stream())
+          int(gate_col) if gates is not None else -1, float(mult), out.data_ptr(), T, H, R, dv, dtype_code(ctx.dtype),
+          single_step.token_seg.data_ptr() if single_step is not None else None,
+          single_step.seg_start.data_ptr() if single_step is not None else None, _stream())
+    return out
+
+
+LATENT_PORTION_TILE = 64           # queries of one CTA of the portion kernel
+LATENT_PORTION_MAX_QK, LATENT_PORTION_MAX_V = 512, 128
+
+
+def latent_portion_build(d: int, dr: int, dv: int, kv_rank: int):
+    """The build of the portion kernel that takes heads of d + dr key channels and dv value channels, as the defines
+    of its module; None where the sizes are not multiples of 8 or beyond what the kernel holds in registers."""
+    if min(d, dr, dv, kv_rank) <= 0 or d % 8 or dr % 8 or dv % 8 or kv_rank % 8:
+        return None
+    qk, v = -(-(d + dr) // 16) * 16, -(-dv // 16) * 16
+    if qk > LATENT_PORTION_MAX_QK or v > LATENT_PORTION_MAX_V:
+        return None
+    return {"IB_QK_DIM": qk, "IB_V_DIM": v}
+
+
+def latent_gather(cache: torch.Tensor, block_table: torch.Tensor, step, n_portions: int, span: int, window: Optional[int],
+                  kv_rank: int):
+    """The rows that the step's portions (segments longer than one token, in order) can see, out of the pages
+    ``cache`` [pages, page_size, kv_rank + dr] into one region of ``span`` rows per portion: row j of a region is
+    position lo + j, lo = max(0, first position of the portion - window + 1) (0 without a window); rows past the
+    portion's last token are zero. Returns (c [portions * span, kv_rank], r [portions * span, dr])."""
+    _check(cache, "cache", torch.bfloat16)
+    n_pages, page_size, dk = cache.shape
+    dr = dk - kv_rank
+    _check(block_table, "block_table", torch.int32)
+    n = n_portions * span
+    c = torch.empty((n, kv_rank), dtype=cache.dtype, device=cache.device)
+    r = torch.empty((n, dr), dtype=cache.dtype, device=cache.device)
+    f = _fn("latent_pf", "ib_latent_gather", [c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int64,
+                                              c_int, c_int, c_void_p, c_void_p, c_int64, c_void_p, c_void_p])
+    _call(f, cache.data_ptr(), block_table.data_ptr(), block_table.shape[1], step.seg_start.data_ptr(), step.seg_pos0.data_ptr(),
+          step.n_segments, int(span), int(window or 0), page_size, n_pages, int(kv_rank), dr, c.data_ptr(), r.data_ptr(), n,
+          _ptr(step.status), _stream())
+    return c, r
+
+
+def latent_prefill(q: torch.Tensor, cos: Optional[torch.Tensor], sin: Optional[torch.Tensor], layout: str, kv: torch.Tensor,
+                   v_col: int, r: torch.Tensor, gates: Optional[torch.Tensor], gate_col: int, mult: float, step, span: int,
+                   n_heads: int, d: int, dr: int, dv: int, window: Optional[int], scale: float, defines,
+                   out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Attention of the step's portions over per-head keys and values formed from the gathered rows: q [T, heads *
+    (d + dr)] (rotated channels not yet turned), kv [portions * span, ld] with head h's keys at column h * d and its
+    values at v_col + h * dv, r [portions * span, dr]. Writes the rows of the portions' tokens of ``out`` [T, heads *
+    dv]: softmax(q k^T * scale) v, times sigmoid(gates[t, gate_col + head]) (``gates`` None: no gate) and ``mult``.
+    ``defines``: what ``latent_portion_build`` returned for these sizes."""
+    _check(q, "q", torch.bfloat16)
+    T = q.shape[0]
+    _check(q, "q", None, (T, n_heads * (d + dr)))
+    _check(kv, "kv", torch.bfloat16)
+    _check(r, "r", torch.bfloat16, (kv.shape[0], dr))
+    n_rot = 0
+    if cos is not None:
+        n_rot = 2 * cos.shape[1]
+        _check(cos, "cos", torch.float32)
+        _check(sin, "sin", torch.float32, tuple(cos.shape))
+    if gates is not None:
+        _check(gates, "gates", torch.float32)
+        if gates.shape[0] != T or gate_col < 0 or gate_col + n_heads > gates.shape[1]:
+            raise KernelError("the gates lie outside their rows")
+    if out is None:
+        out = torch.empty((T, n_heads * dv), dtype=q.dtype, device=q.device)
+    else:
+        _check(out, "out", q.dtype, (T, n_heads * dv))
+    portions = [n for n in step.seg_lens if n > 1]
+    if kv.shape[0] != len(portions) * span or v_col + n_heads * dv > kv.shape[1]:
+        raise KernelError(f"keys and values of {tuple(kv.shape)} for {len(portions)} portions of {span} rows")
+    n_tiles = sum(-(-n // LATENT_PORTION_TILE) for n in portions)
+    f = _fn("latent_pf", "ib_latent_prefill", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int64, c_int, c_void_p, c_void_p,
+                                               c_int64, c_int, c_float, c_void_p, c_void_p, c_void_p] + [c_int] * 8 + [c_float, c_void_p],
+            defines)
+    _call(f, q.data_ptr(), _ptr(cos), _ptr(sin), ROTATION_LAYOUTS[layout], n_rot, kv.data_ptr(), kv.shape[1], int(v_col), r.data_ptr(),
+          _ptr(gates), gates.shape[1] if gates is not None else 0, int(gate_col) if gates is not None else 0, float(mult), out.data_ptr(),
+          step.seg_start.data_ptr(), step.seg_pos0.data_ptr(), step.n_segments, int(span), n_tiles, n_heads, d, dr, dv,
+          int(window or 0), float(scale), _stream())
     return out
 
 

@@ -15,6 +15,14 @@ weighted sum of the c rows, and Wuv_h is applied to that sum (``ops.latent_outpu
 kv_rank + rot_dim multiply-adds for the score and kv_rank for the value, whatever head_dim and v_head_dim are; no
 per-head key or value is ever formed for a cached position.
 
+That is the form for decoded tokens, which meet every cached row once. A prompt portion of n tokens meets every row n
+times, and pays for the latent width each time; for portions (bfloat16, sizes that are multiples of 8) the rows that
+the step's portions can see are gathered out of the pages, one matrix product with [Wuk; Wuv] forms the per-head keys
+and values of those rows, and a tensor-core kernel runs ordinary attention over them (``ops.latent_gather``,
+``ops.latent_prefill``): head_dim + rot_dim and v_head_dim multiply-adds per (query, key, head). Single tokens in
+the same step keep the latent form; both write the same rows. Which form a token takes depends on the lengths of the
+step's segments alone, and the two differ by rounding only.
+
 Spec keys: hidden_size, num_heads, head_dim, rot_dim, v_head_dim, q_rank, kv_rank, softmax_scale, norm_eps,
 ``position`` (a position part with ``rotary_tables`` / ``layout`` / ``rotary_dims``, or None), ``window`` (None: all
 earlier positions), ``head_gate``, ``out_scale`` (a constant on the result, applied to the gated contexts in float32
@@ -33,6 +41,9 @@ from .. import ops
 from ..config.specs import PartSpec
 from .base import Mixer, PagedKVNeed, build_part, register_mixer
 from .linear import Linear
+
+PORTION_MIN_TOKENS = 4
+PORTION_MAX_BYTES = 2 << 30
 
 _NAMES = {"dq": "dq", "dq_norm": "dq.norm", "uq": "uq", "dkv": "dkv", "dkv_norm": "dkv.norm", "uk": "uk", "uv": "uv", "gate": "g", "o": "o"}
 
@@ -76,7 +87,8 @@ class LatentAttention(Mixer):
         max_dk, max_dv = ops.latent_attention_max_dims() if runtime is not None and torch.cuda.is_available() else (1024, 512)
         if self.dk > max_dk or self.kv_rank > max_dv:
             raise ValueError(f"latent rows of {self.kv_rank} + {self.rot_dim} are beyond what the attention kernel takes ({max_dv} + rest up to {max_dk})")
-        self.down = self.uq = self.o = None
+        self.down = self.uq = self.o = self.up_kv = None
+        self.portion_build = None
         self.w_uk = self.w_uvT = self.wq = self.wkv = None
         self.q_col = self.kv_col = self.gate_col = 0
 
@@ -131,12 +143,34 @@ class LatentAttention(Mixer):
         dev = dict(device=self.rt.device, dtype=self.rt.dtype)
         self.w_uk = params[n["uk"]].to(**dev).contiguous()                                   # [heads * head_dim, kv_rank]
         self.w_uvT = params[n["uv"]].to(**dev).view(self.n_heads, self.v_dim, self.kv_rank).transpose(1, 2).contiguous()
+        if self.rt.dtype == torch.bfloat16 and self.rot_dim > 0:
+            self.portion_build = ops.latent_portion_build(self.head_dim, self.rot_dim, self.v_dim, self.kv_rank)
+        if self.portion_build is not None:
+            self.up_kv = Linear(self.rt, torch.cat([params[n["uk"]], params[n["uv"]]], dim=0))   # [heads * (head_dim + v_dim), kv_rank]
         f32 = dict(device=self.rt.device, dtype=torch.float32)
         self.wq = params[n["dq_norm"]].to(**f32).contiguous()
         self.wkv = params[n["dkv_norm"]].to(**f32).contiguous() if self.own_latent else None
 
     def cache_need(self):
         return PagedKVNeed(1, self.dk, self.cache_window, self.kv_rank, values_in_keys=True)
+
+    def _portion_span(self, step, table, pages) -> int:
+        """Rows per portion for the form with per-head keys and values, or 0 where the step takes the latent form for
+        all its tokens: no build for these sizes, fewer than PORTION_MIN_TOKENS tokens in portions (forming the keys
+        of a long context costs more than a few queries over its latent rows), or regions beyond PORTION_MAX_BYTES.
+        Only what a captured step keeps fixed enters: the segments' lengths and the table's width."""
+        if self.portion_build is None or step.max_q_len <= 1:
+            return 0
+        portions = [n for n in step.seg_lens if n > 1]
+        if sum(portions) < PORTION_MIN_TOKENS:
+            return 0
+        span = table.shape[1] * pages.shape[1]
+        if self.window is not None:
+            span = min(span, self.window - 1 + max(portions))
+        width = self.n_heads * (self.head_dim + self.v_dim) + self.dk
+        if len(portions) * span * width * 2 > PORTION_MAX_BYTES:
+            return 0
+        return span
 
     def forward(self, x, step, cache, residual, write_cache=True):
         if write_cache and not self.own_latent:
@@ -152,9 +186,24 @@ class LatentAttention(Mixer):
         cq = ops.latent_prepare(rows, self.q_col, self.q_rank, self.kv_col, self.kv_rank, self.rot_dim, self.wq, self.wkv, self.eps,
                                 cos, sin, layout, step, table, pages, self.rt.dtype, write_cache and self.own_latent)
         q = self.uq(cq)
-        q_lat = ops.latent_query(q, self.w_uk, cos, sin, layout, step.positions, self.n_heads, self.head_dim, self.rot_dim)
-        ctx = ops.latent_attention(q_lat, pages, table, step, self.kv_rank, self.window, self.scale)
-        heads = ops.latent_output(ctx, self.w_uvT, rows if self.head_gate else None, self.gate_col, self.out_scale)
+        gates = rows if self.head_gate else None
+        span = self._portion_span(step, table, pages)
+        if span:
+            # portions: per-head keys and values of the rows they can see, ordinary attention on the tensor cores
+            n_portions = sum(1 for n in step.seg_lens if n > 1)
+            c_rows, r_rows = ops.latent_gather(pages, table, step, n_portions, span, self.window, self.kv_rank)
+            kv = self.up_kv(c_rows)
+            heads = ops.latent_prefill(q, cos, sin, layout, kv, self.n_heads * self.head_dim, r_rows, gates, self.gate_col, self.out_scale,
+                                       step, span, self.n_heads, self.head_dim, self.rot_dim, self.v_dim, self.window, self.scale,
+                                       self.portion_build)
+            if any(n == 1 for n in step.seg_lens):
+                q_lat = ops.latent_query(q, self.w_uk, cos, sin, layout, step.positions, self.n_heads, self.head_dim, self.rot_dim, step)
+                ctx = ops.latent_attention(q_lat, pages, table, step, self.kv_rank, self.window, self.scale, single_only=True)
+                ops.latent_output(ctx, self.w_uvT, gates, self.gate_col, self.out_scale, heads, step)
+        else:
+            q_lat = ops.latent_query(q, self.w_uk, cos, sin, layout, step.positions, self.n_heads, self.head_dim, self.rot_dim)
+            ctx = ops.latent_attention(q_lat, pages, table, step, self.kv_rank, self.window, self.scale)
+            heads = ops.latent_output(ctx, self.w_uvT, gates, self.gate_col, self.out_scale)
         if residual is None:
             return self.o(heads, out_dtype=torch.float32)
         return self.o(heads, residual=residual)

@@ -172,9 +172,12 @@ def test_the_design_runs_on_its_own_kernels():
     before = dict(ops.LAUNCH_KINDS)
     H.run_trace(eng, [{"entries": [("x", ids[:139], [138])], "end": []}, {"entries": [("x", ids[139:], [0])], "end": ["x"]}])
     ran = {k: v - before.get(k, 0) for k, v in ops.LAUNCH_KINDS.items() if v != before.get(k, 0)}
-    for kind in ("ib_layer_norm", "ib_latent_prepare", "ib_latent_query", "ib_latent_attention", "ib_latent_output", "ib_route_sigmoid",
-                 "ib_scaled_relu_sq", "ib_scale_softcap"):
+    for kind in ("ib_layer_norm", "ib_latent_prepare", "ib_route_sigmoid", "ib_scaled_relu_sq", "ib_scale_softcap"):
         assert ran.get(kind, 0) >= 2, (kind, ran)
+    for kind in ("ib_latent_gather", "ib_latent_prefill"):   # the prompt: per-head keys and values on the tensor cores
+        assert ran.get(kind, 0) >= 3, (kind, ran)
+    for kind in ("ib_latent_query", "ib_latent_attention", "ib_latent_output"):   # the decoded token: the latent form
+        assert ran.get(kind, 0) >= 3, (kind, ran)
     assert ran.get("ib_gemm_tc", 0) >= 1                     # the tensor-core product serves the prompt's matrices
     assert "ib_attention_plain" not in ran
 
