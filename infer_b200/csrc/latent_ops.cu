@@ -129,15 +129,16 @@ latent_prepare_kernel(const float* __restrict__ rows, int64_t ld, int q_col, int
 
 // ------------------------------------------------------------------------------------------------
 // Products of a step's rows with one small matrix per head: out[t, h, n] = sum_k a[t, h, k] * B[h][k][n], B row-major
-// with n contiguous. One CTA of 256 threads per (HP_TOK tokens, head, tile of 16 * C columns), C = 16 bytes of T per
-// thread. A thread owns C neighbouring columns of every token and every 16th k (k = slice, slice + 16, ...), so a
-// matrix row is read once, by 16-byte loads, for all HP_TOK tokens; the 16 slice sums of a column are added in slice
-// order (pairs by a shuffle, then the eight warps in order through shared memory). The order of a sum depends on k
+// with n contiguous. One CTA of 256 threads per (HP_TOK tokens, head, tile of HP_CL * C columns), C = 16 bytes of T per
+// thread: narrow tiles, so that a step of few tokens still spreads a head's matrix over many CTAs. A thread owns C
+// neighbouring columns of every token and every 64th k (k = slice, slice + 64, ...), so a matrix row is read once, by
+// 16-byte loads, for all HP_TOK tokens; the 64 slice sums of a column are added in a fixed order (the eight slices of
+// a warp by shuffles, then the eight warps in order through shared memory). The order of a sum depends on k
 // alone: a token's result does not depend on which other tokens share its CTA. Leaves the eight warps' partial sums
-// in `red` [8][HP_TOK][16 * C] behind a barrier.
+// in `red` [8][HP_TOK][HP_CL * C] behind a barrier.
 // With `seg_start` the CTAs serve the tokens of one-token segments only: rows of longer segments are neither read nor
 // written (their attention runs elsewhere).
-constexpr int HP_TOK = 8, HP_THREADS = 256, HP_CL = 16, HP_KS = HP_THREADS / HP_CL, HP_WARPS = HP_THREADS / 32;
+constexpr int HP_TOK = 8, HP_THREADS = 256, HP_CL = 4, HP_KS = HP_THREADS / HP_CL, HP_WARPS = HP_THREADS / 32;
 
 template <typename T>
 struct HpCols { static constexpr int v = 16 / int(sizeof(T)); };
@@ -194,8 +195,11 @@ __device__ __forceinline__ void head_product_tile(const float* __restrict__ a_s,
 #pragma unroll
     for (int tt = 0; tt < HP_TOK; tt++)
 #pragma unroll
-        for (int c = 0; c < C; c++) acc[tt][c] += __shfl_xor_sync(0xffffffffu, acc[tt][c], 16);
-    if (lane < 16) {
+        for (int c = 0; c < C; c++) {
+#pragma unroll
+            for (int off = HP_CL; off < 32; off *= 2) acc[tt][c] += __shfl_xor_sync(0xffffffffu, acc[tt][c], off);
+        }
+    if (lane < HP_CL) {
 #pragma unroll
         for (int tt = 0; tt < HP_TOK; tt++)
 #pragma unroll
@@ -497,6 +501,189 @@ latent_attention_kernel(const T* __restrict__ q, const T* __restrict__ cache, co
     }
 }
 
+// ------------------------------------------------------------------------------------------------
+// The same attention for single tokens in bfloat16 on the tensor cores (mma.sync m16n8k16): the heads of a token are
+// the rows of the tile. One CTA of four warps per (token, group of 16 heads, chunk of TC_KC keys aligned to absolute
+// multiples of TC_KC); it always leaves (m, l, o) in `parts`, and the merge kernel follows. The chunk's rows come
+// into shared memory by 16-byte asynchronous copies (dk a multiple of 8), rows outside [lo, pos] as zeros; they serve
+// as keys (all dk channels) and as values (the first dv). Warp w computes the scores of keys 16 w .. 16 w + 15, the
+// maxima and sums cross the warps through shared memory, the probabilities are left there as two bfloat16 terms
+// (p = hi + lo), and warp w then sums channels [16 NV w, 16 NV (w + 1)) over all keys.
+constexpr int TC_KC = 64, TC_THREADS = 128, TC_HEADS = 16, TC_PS = TC_KC + 8;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return uint32_t(__cvta_generic_to_shared(p)); }
+__device__ __forceinline__ void ldsm4(uint32_t addr, uint32_t (&r)[4]) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm4_t(uint32_t addr, uint32_t (&r)[4]) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void mma16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, int bytes) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() {
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+}
+__device__ __forceinline__ void split_bf16(float x, bf16& hi, bf16& lo) {
+    hi = __float2bfloat16_rn(x);
+    lo = __float2bfloat16_rn(x - __bfloat162float(hi));
+}
+
+// row stride of the chunk's rows in shared memory: dk rounded up to 16, plus 8 (an odd number of 16-byte units)
+__host__ __device__ inline int tc_row_stride(int dk) { return ((dk + 15) & ~15) + 8; }
+
+template <int NV>
+__global__ void __launch_bounds__(TC_THREADS)
+latent_attention_tc_kernel(const bf16* __restrict__ q, const bf16* __restrict__ cache, const int* __restrict__ block_table,
+                           int64_t max_blocks, const int* __restrict__ token_seg, const int* __restrict__ positions,
+                           float* __restrict__ parts, int n_heads, int dk, int dv, int page_size, int window, float scale,
+                           int64_t n_pages, int n_splits, int* status, const int* __restrict__ seg_start) {
+    ib::pdl_wait();
+    const int64_t t = blockIdx.x;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    if (seg_start) {
+        const int sg = token_seg[t];
+        if (seg_start[sg + 1] - seg_start[sg] != 1) return;
+    }
+    const int pos = positions[t];
+    const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+    const int ch = lo / TC_KC + int(blockIdx.z);
+    if (ch > pos / TC_KC) return;
+    const int h0 = blockIdx.y * TC_HEADS, ng = min(TC_HEADS, n_heads - h0);
+    const int RS = tc_row_stride(dk), dkp = RS - 8;
+    extern __shared__ __align__(16) unsigned char tc_sm[];
+    bf16* Qs = reinterpret_cast<bf16*>(tc_sm);               // [16][RS]
+    bf16* Ks = Qs + TC_HEADS * RS;                           // [TC_KC][RS] (+ slack for the last warp's channel tiles)
+    bf16* Ph = Ks + TC_KC * RS + 64 * NV;                 // [16][TC_PS]
+    bf16* Pl = Ph + TC_HEADS * TC_PS;                        // [16][TC_PS]
+    float* red = reinterpret_cast<float*>(Pl + TC_HEADS * TC_PS);   // [2][4][16] maxima, sums
+    const int* table = block_table + int64_t(token_seg[t]) * max_blocks;
+    const int cpr = dkp / 8, base = ch * TC_KC;
+    for (int i = tid; i < TC_KC * cpr; i += TC_THREADS) {
+        const int row = i / cpr, e = (i - row * cpr) * 8, key = base + row;
+        const bf16* src = cache;
+        int bytes = 0;
+        if (key >= lo && key <= pos && e < dk) {
+            const int page = table[key / page_size];
+            if (page < 0 || page >= n_pages) {
+                if (status) atomicExch(status, 3);
+            } else {
+                src = cache + (int64_t(page) * page_size + key % page_size) * dk + e;
+                bytes = 16;
+            }
+        }
+        cp_async16(smem_u32(Ks + row * RS + e), src, bytes);
+    }
+    for (int i = tid; i < TC_HEADS * cpr; i += TC_THREADS) {
+        const int row = i / cpr, e = (i - row * cpr) * 8;
+        const bool on = row < ng && e < dk;
+        cp_async16(smem_u32(Qs + row * RS + e), on ? q + (t * n_heads + h0 + row) * dk + e : q, on ? 16 : 0);
+    }
+    cp_async_wait_all();
+    __syncthreads();
+    // scores of this warp's 16 keys for all 16 heads
+    float sc[2][4];
+#pragma unroll
+    for (int i = 0; i < 2; i++) sc[i][0] = sc[i][1] = sc[i][2] = sc[i][3] = 0.0f;
+    for (int ks = 0; ks < dkp / 16; ks++) {
+        uint32_t a[4], b[4];
+        ldsm4(smem_u32(Qs + (lane & 15) * RS + ks * 16 + (lane >> 4) * 8), a);
+        ldsm4(smem_u32(Ks + (warp * 16 + (lane & 7) + (lane >> 4) * 8) * RS + ks * 16 + ((lane >> 3) & 1) * 8), b);
+        mma16816(sc[0], a, b[0], b[1]);
+        mma16816(sc[1], a, b[2], b[3]);
+    }
+    // rows lane / 4 and lane / 4 + 8 (heads), columns: keys base + 16 warp + 8 nt + 2 (lane % 4) + {0, 1}
+    float mx_a = -INFINITY, mx_b = -INFINITY;
+#pragma unroll
+    for (int nt = 0; nt < 2; nt++) {
+#pragma unroll
+        for (int c = 0; c < 4; c++) {
+            const int key = base + warp * 16 + nt * 8 + (lane & 3) * 2 + (c & 1);
+            const float v = (key >= lo && key <= pos) ? sc[nt][c] * scale : -INFINITY;
+            sc[nt][c] = v;
+            if (c < 2) mx_a = fmaxf(mx_a, v); else mx_b = fmaxf(mx_b, v);
+        }
+    }
+    mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 1));
+    mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 2));
+    mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 1));
+    mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 2));
+    const int ra = lane >> 2, rb = ra + 8;
+    if ((lane & 3) == 0) { red[warp * 16 + ra] = mx_a; red[warp * 16 + rb] = mx_b; }
+    __syncthreads();
+    float m_a = -INFINITY, m_b = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < 4; w++) { m_a = fmaxf(m_a, red[w * 16 + ra]); m_b = fmaxf(m_b, red[w * 16 + rb]); }
+    const float ba = m_a == -INFINITY ? 0.0f : m_a, bb = m_b == -INFINITY ? 0.0f : m_b;
+    float sum_a = 0.0f, sum_b = 0.0f;
+#pragma unroll
+    for (int nt = 0; nt < 2; nt++) {
+#pragma unroll
+        for (int c = 0; c < 4; c++) {
+            const float pv = sc[nt][c] > -INFINITY ? expf(sc[nt][c] - (c < 2 ? ba : bb)) : 0.0f;
+            if (c < 2) sum_a += pv; else sum_b += pv;
+            const int col = warp * 16 + nt * 8 + (lane & 3) * 2 + (c & 1), row = c < 2 ? ra : rb;
+            bf16 hi, lw;
+            split_bf16(pv, hi, lw);
+            Ph[row * TC_PS + col] = hi;
+            Pl[row * TC_PS + col] = lw;
+        }
+    }
+    sum_a += __shfl_xor_sync(0xffffffffu, sum_a, 1);
+    sum_a += __shfl_xor_sync(0xffffffffu, sum_a, 2);
+    sum_b += __shfl_xor_sync(0xffffffffu, sum_b, 1);
+    sum_b += __shfl_xor_sync(0xffffffffu, sum_b, 2);
+    if ((lane & 3) == 0) { red[64 + warp * 16 + ra] = sum_a; red[64 + warp * 16 + rb] = sum_b; }
+    __syncthreads();
+    // O = P V for this warp's channels
+    float o[2 * NV][4];
+#pragma unroll
+    for (int i = 0; i < 2 * NV; i++) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
+    const int c0 = warp * NV * 16;
+    if (c0 < dv) {
+#pragma unroll
+        for (int kk = 0; kk < TC_KC / 16; kk++) {
+            uint32_t ph[4], pl[4];
+            ldsm4(smem_u32(Ph + (lane & 15) * TC_PS + kk * 16 + (lane >> 4) * 8), ph);
+            ldsm4(smem_u32(Pl + (lane & 15) * TC_PS + kk * 16 + (lane >> 4) * 8), pl);
+#pragma unroll
+            for (int np = 0; np < NV; np++) {
+                uint32_t b[4];
+                ldsm4_t(smem_u32(Ks + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * RS + c0 + np * 16 + (lane >> 4) * 8), b);
+                mma16816(o[2 * np], ph, b[0], b[1]);
+                mma16816(o[2 * np + 1], ph, b[2], b[3]);
+                mma16816(o[2 * np], pl, b[0], b[1]);
+                mma16816(o[2 * np + 1], pl, b[2], b[3]);
+            }
+        }
+    }
+#pragma unroll
+    for (int half_i = 0; half_i < 2; half_i++) {
+        const int row = half_i ? rb : ra;
+        if (row >= ng) continue;
+        float* dst = parts + ((t * n_heads + h0 + row) * n_splits + blockIdx.z) * int64_t(dv + 2);
+        if (warp == 0 && (lane & 3) == 0) {
+            float l = 0.0f;
+#pragma unroll
+            for (int w = 0; w < 4; w++) l += red[64 + w * 16 + row];
+            dst[0] = half_i ? m_b : m_a;
+            dst[1] = l;
+        }
+#pragma unroll
+        for (int i = 0; i < 2 * NV; i++) {
+            const int col = c0 + i * 8 + (lane & 3) * 2;
+            if (col < dv) dst[2 + col] = o[i][2 * half_i];
+            if (col + 1 < dv) dst[2 + col + 1] = o[i][2 * half_i + 1];
+        }
+    }
+}
+
 // One CTA per (token, head), one thread per channel: the chunks' parts merged in ascending order, then the division.
 // The chunks' maxima and sums wait in shared memory; every thread walks the same chain over them, and its own loads
 // of the parts' channels do not depend on the chain, so they are in flight together.
@@ -505,7 +692,7 @@ constexpr int MG_THREADS = 128, MG_STAGE = 256;
 template <typename T>
 __global__ void __launch_bounds__(MG_THREADS)
 latent_attention_merge_kernel(const float* __restrict__ parts, const int* __restrict__ positions, T* __restrict__ out,
-                              int n_heads, int dv, int window, int n_splits, const int* __restrict__ token_seg,
+                              int n_heads, int dv, int window, int n_splits, int chunk, const int* __restrict__ token_seg,
                               const int* __restrict__ seg_start) {
     ib::pdl_wait();
     __shared__ float ml_s[2 * MG_STAGE];
@@ -517,7 +704,7 @@ latent_attention_merge_kernel(const float* __restrict__ parts, const int* __rest
     }
     const int pos = positions[t];
     const int lo = window > 0 ? max(0, pos - window + 1) : 0;
-    const int n = min(n_splits, pos / KC - lo / KC + 1);
+    const int n = min(n_splits, pos / chunk - lo / chunk + 1);
     const int stride = dv + 2;
     const float* mine = parts + r * n_splits * int64_t(stride);
     const bool staged = n <= MG_STAGE;
@@ -792,12 +979,36 @@ int pick_latent_attention(int gb, int nc, const void* q, const void* cache, cons
 IB_EXPORT int ib_latent_attention(const void* q, const void* cache, const int* block_table, int64_t max_blocks, const int* token_seg,
                                   const int* positions, void* out, float* parts, int64_t n_tokens, int n_heads, int dk, int dv,
                                   int page_size, int window, float scale, int64_t n_pages, int n_splits, int dtype, int* status,
-                                  const int* single_start, cudaStream_t stream) {
+                                  const int* single_start, int chunk, cudaStream_t stream) {
     if (n_tokens <= 0) return IB_OK;
+    if (chunk != KC && chunk != TC_KC) return ib::fail(IB_ERR_ARG, "ib_latent_attention: chunks of %d keys", chunk);
     if (n_heads <= 0 || dk <= 0 || dk > 1024 || dv <= 0 || dv > dk || dv > 4 * KC)
         return ib::fail(IB_ERR_ARG, "ib_latent_attention: %d heads, rows of %d with values of %d are outside what the kernel takes", n_heads, dk, dv);
     if (n_splits < 1 || (n_splits > 1 && !parts)) return ib::fail(IB_ERR_ARG, "ib_latent_attention: %d splits need a workspace", n_splits);
     if (n_splits > 65535 || (n_heads + GMAX - 1) / GMAX > 65535) return ib::fail(IB_ERR_ARG, "ib_latent_attention: grid too large");
+    if (chunk == TC_KC) {
+        // chunks of 64 keys: the tensor-core kernel, which always leaves parts for the merge
+        if (dtype != IB_BF16 || dk % 8 || dv > 512 || !parts)
+            return ib::fail(IB_ERR_ARG, "ib_latent_attention: the tensor-core kernel takes bfloat16 rows of a multiple of 8 channels, values up to 512 and a workspace");
+        const int nv = dv <= 64 ? 1 : dv <= 128 ? 2 : dv <= 256 ? 4 : 8;
+        const int RS = tc_row_stride(dk);
+        const size_t smem = (size_t(TC_HEADS + TC_KC) * RS + 64 * nv + 2 * TC_HEADS * TC_PS) * sizeof(bf16) + 128 * sizeof(float);
+        const dim3 grid{unsigned(n_tokens), unsigned((n_heads + TC_HEADS - 1) / TC_HEADS), unsigned(n_splits)};
+#define IB_TC(NV_)                                                                                                            \
+    if (nv == NV_) {                                                                                                          \
+        const int rc = allow_smem(latent_attention_tc_kernel<NV_>, smem);                                                     \
+        if (rc) return rc;                                                                                                    \
+        IB_LAUNCH(latent_attention_tc_kernel<NV_>, grid, TC_THREADS, smem, (const bf16*)q, (const bf16*)cache, block_table, max_blocks, \
+                  token_seg, positions, parts, n_heads, dk, dv, page_size, window, scale, n_pages, n_splits, status, single_start); \
+    }
+        IB_TC(1) IB_TC(2) IB_TC(4) IB_TC(8)
+#undef IB_TC
+        const int64_t n_rows = n_tokens * n_heads;
+        if (n_rows > 0x7fffffff) return ib::fail(IB_ERR_ARG, "ib_latent_attention: too many rows to merge");
+        IB_LAUNCH(latent_attention_merge_kernel<bf16>, unsigned(n_rows), MG_THREADS, 0, parts, positions, (bf16*)out, n_heads, dv, window,
+                  n_splits, chunk, token_seg, single_start);
+        return ib::check_launch("ib_latent_attention");
+    }
     const int group = n_heads < GMAX ? n_heads : GMAX;
     const int gb = group <= 1 ? 1 : group <= 2 ? 2 : group <= 4 ? 4 : 8;
     const int passes = (dv + KC - 1) / KC, nc = passes <= 1 ? 1 : passes <= 2 ? 2 : 4;
@@ -816,10 +1027,10 @@ IB_EXPORT int ib_latent_attention(const void* q, const void* cache, const int* b
         if (n_rows > 0x7fffffff) return ib::fail(IB_ERR_ARG, "ib_latent_attention: too many rows to merge");
         if (dtype == IB_F32)
             IB_LAUNCH(latent_attention_merge_kernel<float>, unsigned(n_rows), MG_THREADS, 0, parts, positions, (float*)out, n_heads, dv,
-                      window, n_splits, token_seg, single_start);
+                      window, n_splits, chunk, token_seg, single_start);
         else
             IB_LAUNCH(latent_attention_merge_kernel<bf16>, unsigned(n_rows), MG_THREADS, 0, parts, positions, (bf16*)out, n_heads, dv,
-                      window, n_splits, token_seg, single_start);
+                      window, n_splits, chunk, token_seg, single_start);
     }
     return ib::check_launch("ib_latent_attention");
 }

@@ -58,6 +58,13 @@ __device__ __forceinline__ void mma16816(float (&c)[4], const uint32_t (&a)[4], 
                  : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
+// 16 bytes from global to shared memory without passing registers; `bytes` 0: sixteen zero bytes, nothing is read
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, int bytes) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
     const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<const uint32_t*>(&v);
@@ -148,6 +155,7 @@ latent_prefill_kernel(const bf16* __restrict__ q, const float* __restrict__ cos_
         p++;
     }
     if (s < 0) return;
+    tile = (len + BM - 1) / BM - 1 - tile;                   // a portion's last queries see the most keys: they start first
     const int q0 = tile * BM, t0 = seg_start[s] + q0, pos0 = seg_pos0[s];
     const int nq = min(BM, len - q0);
     const int lo = window > 0 ? max(0, pos0 - window + 1) : 0;
@@ -188,110 +196,151 @@ latent_prefill_kernel(const bf16* __restrict__ q, const float* __restrict__ cos_
 
     const int ra = warp * 16 + (lane >> 2), rb = ra + 8;     // this thread's two query rows of the tile
     const int qpa = ra < nq ? qp_first + ra : -1, qpb = rb < nq ? qp_first + rb : -1;
+    const int wq_min = qp_first + warp * 16, wq_max = min(wq_min + 15, qp_last);   // the warp's query positions
+    const bool warp_full = warp * 16 + 15 < nq;
+    const float sl2 = scale * LOG2E;                         // scores are kept times log2(e): exponentials are exp2
     float m_a = -INFINITY, m_b = -INFINITY, l_a = 0.0f, l_b = 0.0f;
     float o[DV / 8][4];
 #pragma unroll
     for (int i = 0; i < DV / 8; i++) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
 
-    for (int jt = j_first / BN; jt <= j_last / BN; jt++) {
+    // K and V tiles have one buffer each and are asked for one tile ahead: K(j + 1) as soon as S(j) has been
+    // computed, V(j + 1) as soon as P(j) V(j) has; each request is one cp.async group.
+    const int64_t region = int64_t(p) * span;
+    auto load_k = [&](int j0) {
+        constexpr int cpr = DQK / 8;
+        for (int i = tid; i < BN * cpr; i += PF_THREADS) {
+            const int row = i / cpr, e = (i - row * cpr) * 8, j = j0 + row;
+            const bf16* src = kv;
+            int bytes = 0;
+            if (j < span) {
+                const int64_t g = region + j;
+                if (e < d) { src = kv + g * ld_kv + h * d + e; bytes = 16; }
+                else if (e < dh) { src = r + g * dr + (e - d); bytes = 16; }
+            }
+            cp_async16(smem_u32(Ks + row * QS + e), src, bytes);
+        }
+        cp_async_commit();
+    };
+    auto load_v = [&](int j0) {
+        constexpr int vpr = DV / 8;
+        for (int i = tid; i < BN * vpr; i += PF_THREADS) {
+            const int row = i / vpr, e = (i - row * vpr) * 8, j = j0 + row;
+            const bf16* src = kv;
+            int bytes = 0;
+            if (j < span && e < dv) { src = kv + (region + j) * ld_kv + v_col + h * dv + e; bytes = 16; }
+            cp_async16(smem_u32(Vs + row * VS + e), src, bytes);
+        }
+        cp_async_commit();
+    };
+    const int jt_first = j_first / BN, jt_last = j_last / BN;
+    load_k(jt_first * BN);
+    load_v(jt_first * BN);
+    for (int jt = jt_first; jt <= jt_last; jt++) {
         const int j0 = jt * BN;
-        __syncthreads();                                     // the last tile has been read (and Q has been written)
-        {
-            const int cpr = DQK / 8;
-            for (int i = tid; i < BN * cpr; i += PF_THREADS) {
-                const int row = i / cpr, e = (i - row * cpr) * 8, j = j0 + row;
-                uint4 v = zero4;
-                if (j < span) {
-                    const int64_t g = int64_t(p) * span + j;
-                    if (e < d) v = *reinterpret_cast<const uint4*>(kv + g * ld_kv + h * d + e);
-                    else if (e < dh) v = *reinterpret_cast<const uint4*>(r + g * dr + (e - d));
-                }
-                *reinterpret_cast<uint4*>(Ks + row * QS + e) = v;
-            }
-            const int vpr = DV / 8;
-            for (int i = tid; i < BN * vpr; i += PF_THREADS) {
-                const int row = i / vpr, e = (i - row * vpr) * 8, j = j0 + row;
-                uint4 v = zero4;
-                if (j < span && e < dv) v = *reinterpret_cast<const uint4*>(kv + (int64_t(p) * span + j) * ld_kv + v_col + h * dv + e);
-                *reinterpret_cast<uint4*>(Vs + row * VS + e) = v;
-            }
-        }
+        const int kp_lo = lo + j0, kp_hi = kp_lo + BN - 1;
+        // the warp's part of this tile: nothing visible, everything visible, or masked element by element
+        const bool none = kp_lo > wq_max || (window > 0 && wq_min - kp_hi >= window);
+        const bool all = warp_full && kp_hi <= wq_min && (window <= 0 || wq_max - kp_lo < window) && j0 + BN <= span;
+        cp_async_wait<1>();                                  // K(j) has arrived (V(j) may still be on its way)
         __syncthreads();
-        // S = Q K^T
         float sc[BN / 8][4];
+        if (!none) {
 #pragma unroll
-        for (int i = 0; i < BN / 8; i++) sc[i][0] = sc[i][1] = sc[i][2] = sc[i][3] = 0.0f;
+            for (int i = 0; i < BN / 8; i++) sc[i][0] = sc[i][1] = sc[i][2] = sc[i][3] = 0.0f;
 #pragma unroll 2
-        for (int ks = 0; ks < DQK / 16; ks++) {
-            uint32_t a[4];
-            ldsm4(smem_u32(Qs + (warp * 16 + (lane & 15)) * QS + ks * 16 + (lane >> 4) * 8), a);
+            for (int ks = 0; ks < DQK / 16; ks++) {
+                uint32_t a[4];
+                ldsm4(smem_u32(Qs + (warp * 16 + (lane & 15)) * QS + ks * 16 + (lane >> 4) * 8), a);
 #pragma unroll
-            for (int np = 0; np < BN / 16; np++) {
-                uint32_t b[4];
-                ldsm4(smem_u32(Ks + (np * 16 + (lane & 7) + (lane >> 4) * 8) * QS + ks * 16 + ((lane >> 3) & 1) * 8), b);
-                mma16816(sc[2 * np], a, b[0], b[1]);
-                mma16816(sc[2 * np + 1], a, b[2], b[3]);
+                for (int np = 0; np < BN / 16; np++) {
+                    uint32_t b[4];
+                    ldsm4(smem_u32(Ks + (np * 16 + (lane & 7) + (lane >> 4) * 8) * QS + ks * 16 + ((lane >> 3) & 1) * 8), b);
+                    mma16816(sc[2 * np], a, b[0], b[1]);
+                    mma16816(sc[2 * np + 1], a, b[2], b[3]);
+                }
             }
         }
-        // mask, running maximum and sum
-        const int kp0 = lo + j0 + (lane & 3) * 2;
-        float mx_a = -INFINITY, mx_b = -INFINITY;
+        __syncthreads();                                     // every warp has read K(j)
+        if (jt < jt_last) load_k(j0 + BN); else cp_async_commit();
+        float al_a = 1.0f, al_b = 1.0f;
+        if (!none) {
+            float mx_a = -INFINITY, mx_b = -INFINITY;
+            if (all) {
 #pragma unroll
-        for (int nt = 0; nt < BN / 8; nt++) {
+                for (int nt = 0; nt < BN / 8; nt++) {
 #pragma unroll
-            for (int c = 0; c < 4; c++) {
-                const int kp = kp0 + nt * 8 + (c & 1), qp = c < 2 ? qpa : qpb;
-                const bool vis = kp <= qp && (window <= 0 || qp - kp < window) && kp - lo < span;
-                const float v = vis ? sc[nt][c] * scale : -INFINITY;
-                sc[nt][c] = v;
-                if (c < 2) mx_a = fmaxf(mx_a, v); else mx_b = fmaxf(mx_b, v);
+                    for (int c = 0; c < 4; c++) sc[nt][c] *= sl2;
+                    mx_a = fmaxf(mx_a, fmaxf(sc[nt][0], sc[nt][1]));
+                    mx_b = fmaxf(mx_b, fmaxf(sc[nt][2], sc[nt][3]));
+                }
+            } else {
+                const int kp0 = kp_lo + (lane & 3) * 2;
+#pragma unroll
+                for (int nt = 0; nt < BN / 8; nt++) {
+#pragma unroll
+                    for (int c = 0; c < 4; c++) {
+                        const int kp = kp0 + nt * 8 + (c & 1), qp = c < 2 ? qpa : qpb;
+                        const bool vis = kp <= qp && (window <= 0 || qp - kp < window) && kp - lo < span;
+                        const float v = vis ? sc[nt][c] * sl2 : -INFINITY;
+                        sc[nt][c] = v;
+                        if (c < 2) mx_a = fmaxf(mx_a, v); else mx_b = fmaxf(mx_b, v);
+                    }
+                }
+            }
+            mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 1));
+            mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 2));
+            mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 1));
+            mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 2));
+            const float mn_a = fmaxf(m_a, mx_a), mn_b = fmaxf(m_b, mx_b);
+            al_a = m_a == -INFINITY ? 0.0f : exp2f(m_a - mn_a);
+            al_b = m_b == -INFINITY ? 0.0f : exp2f(m_b - mn_b);
+            const float ba = mn_a == -INFINITY ? 0.0f : mn_a, bb = mn_b == -INFINITY ? 0.0f : mn_b;
+            m_a = mn_a;
+            m_b = mn_b;
+            float sum_a = 0.0f, sum_b = 0.0f;
+#pragma unroll
+            for (int nt = 0; nt < BN / 8; nt++) {
+                sc[nt][0] = exp2f(sc[nt][0] - ba);           // exp2(-inf) = 0 for what is masked
+                sc[nt][1] = exp2f(sc[nt][1] - ba);
+                sc[nt][2] = exp2f(sc[nt][2] - bb);
+                sc[nt][3] = exp2f(sc[nt][3] - bb);
+                sum_a += sc[nt][0] + sc[nt][1];
+                sum_b += sc[nt][2] + sc[nt][3];
+            }
+            l_a = l_a * al_a + sum_a;
+            l_b = l_b * al_b + sum_b;
+#pragma unroll
+            for (int i = 0; i < DV / 8; i++) {
+                o[i][0] *= al_a; o[i][1] *= al_a; o[i][2] *= al_b; o[i][3] *= al_b;
             }
         }
-        mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 1));
-        mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 2));
-        mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 1));
-        mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 2));
-        const float mn_a = fmaxf(m_a, mx_a), mn_b = fmaxf(m_b, mx_b);
-        const float al_a = m_a == -INFINITY ? 0.0f : exp2f((m_a - mn_a) * LOG2E);
-        const float al_b = m_b == -INFINITY ? 0.0f : exp2f((m_b - mn_b) * LOG2E);
-        const float ba = mn_a == -INFINITY ? 0.0f : mn_a, bb = mn_b == -INFINITY ? 0.0f : mn_b;
-        m_a = mn_a;
-        m_b = mn_b;
-        float sum_a = 0.0f, sum_b = 0.0f;
+        cp_async_wait<1>();                                  // V(j) has arrived (K(j + 1) may still be on its way)
+        __syncthreads();
+        if (!none) {
+            // O += P V, P as two bfloat16 terms
 #pragma unroll
-        for (int nt = 0; nt < BN / 8; nt++) {
-            sc[nt][0] = exp2f((sc[nt][0] - ba) * LOG2E);     // exp2(-inf) = 0 for what is masked
-            sc[nt][1] = exp2f((sc[nt][1] - ba) * LOG2E);
-            sc[nt][2] = exp2f((sc[nt][2] - bb) * LOG2E);
-            sc[nt][3] = exp2f((sc[nt][3] - bb) * LOG2E);
-            sum_a += sc[nt][0] + sc[nt][1];
-            sum_b += sc[nt][2] + sc[nt][3];
-        }
-        l_a = l_a * al_a + sum_a;
-        l_b = l_b * al_b + sum_b;
+            for (int kk = 0; kk < BN / 16; kk++) {
+                uint32_t ph[4], pl[4];
+                split2(sc[2 * kk][0], sc[2 * kk][1], ph[0], pl[0]);
+                split2(sc[2 * kk][2], sc[2 * kk][3], ph[1], pl[1]);
+                split2(sc[2 * kk + 1][0], sc[2 * kk + 1][1], ph[2], pl[2]);
+                split2(sc[2 * kk + 1][2], sc[2 * kk + 1][3], ph[3], pl[3]);
 #pragma unroll
-        for (int i = 0; i < DV / 8; i++) {
-            o[i][0] *= al_a; o[i][1] *= al_a; o[i][2] *= al_b; o[i][3] *= al_b;
-        }
-        // O += P V, P as two bfloat16 terms
-#pragma unroll
-        for (int kk = 0; kk < BN / 16; kk++) {
-            uint32_t ph[4], pl[4];
-            split2(sc[2 * kk][0], sc[2 * kk][1], ph[0], pl[0]);
-            split2(sc[2 * kk][2], sc[2 * kk][3], ph[1], pl[1]);
-            split2(sc[2 * kk + 1][0], sc[2 * kk + 1][1], ph[2], pl[2]);
-            split2(sc[2 * kk + 1][2], sc[2 * kk + 1][3], ph[3], pl[3]);
-#pragma unroll
-            for (int np = 0; np < DV / 16; np++) {
-                uint32_t b[4];
-                ldsm4_t(smem_u32(Vs + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * VS + np * 16 + (lane >> 4) * 8), b);
-                mma16816(o[2 * np], ph, b[0], b[1]);
-                mma16816(o[2 * np + 1], ph, b[2], b[3]);
-                mma16816(o[2 * np], pl, b[0], b[1]);
-                mma16816(o[2 * np + 1], pl, b[2], b[3]);
+                for (int np = 0; np < DV / 16; np++) {
+                    uint32_t b[4];
+                    ldsm4_t(smem_u32(Vs + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * VS + np * 16 + (lane >> 4) * 8), b);
+                    mma16816(o[2 * np], ph, b[0], b[1]);
+                    mma16816(o[2 * np + 1], ph, b[2], b[3]);
+                    mma16816(o[2 * np], pl, b[0], b[1]);
+                    mma16816(o[2 * np + 1], pl, b[2], b[3]);
+                }
             }
         }
+        __syncthreads();                                     // every warp has read V(j)
+        if (jt < jt_last) load_v(j0 + BN); else cp_async_commit();
     }
+    cp_async_wait<0>();
     l_a += __shfl_xor_sync(0xffffffffu, l_a, 1);
     l_a += __shfl_xor_sync(0xffffffffu, l_a, 2);
     l_b += __shfl_xor_sync(0xffffffffu, l_b, 1);

@@ -871,6 +871,8 @@ def latent_attention_max_dims():
 
 
 LATENT_CHUNK = 128                 # keys of one chunk of the latent attention kernel
+LATENT_CHUNK_TC = 64               # ... of its tensor-core form for single tokens
+LATENT_PARTS_MAX_BYTES = 512 << 20
 
 
 def latent_attention(q: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor, step, dv: int, window: Optional[int],
@@ -884,22 +886,31 @@ def latent_attention(q: torch.Tensor, cache: torch.Tensor, block_table: torch.Te
     n_pages, page_size, _ = cache.shape
     _check(cache, "cache", q.dtype, (n_pages, page_size, dk))
     _check(block_table, "block_table", torch.int32)
-    span = step.max_ctx_len if not window else min(step.max_ctx_len, int(window) + LATENT_CHUNK - 1)
-    chunks = max(1, -(-span // LATENT_CHUNK) + (1 if window else 0))
+    singles = T if step.decode_only else sum(1 for n in step.seg_lens if n == 1)
+    # single tokens in bfloat16: chunks of 64 keys on the tensor cores, always spread over CTAs (while the parts fit)
+    chunk = LATENT_CHUNK
+    if q.dtype == torch.bfloat16 and dk % 8 == 0 and dv <= 512 and (step.decode_only or single_only) and split is not False:
+        chunk = LATENT_CHUNK_TC
+    span = step.max_ctx_len if not window else min(step.max_ctx_len, int(window) + chunk - 1)
+    chunks = max(1, -(-span // chunk) + (1 if window else 0))
+    if chunk == LATENT_CHUNK_TC and T * H * chunks * (dv + 2) * 4 > LATENT_PARTS_MAX_BYTES:
+        chunk = LATENT_CHUNK
+        chunks = max(1, -(-(step.max_ctx_len if not window else min(step.max_ctx_len, int(window) + chunk - 1)) // chunk) + (1 if window else 0))
     if split is None:
-        singles = T if step.decode_only else sum(1 for n in step.seg_lens if n == 1)
         split = (step.decode_only or single_only) and singles * ((H + 7) // 8) < 256
-    n_splits = chunks if (split and chunks > 1) else 1
+    n_splits = chunks if (chunk == LATENT_CHUNK_TC or (split and chunks > 1)) else 1
     out = torch.empty((T, H, dv), dtype=q.dtype, device=q.device)
     parts = None
-    if n_splits > 1:
+    if n_splits > 1 or chunk == LATENT_CHUNK_TC:
         from .fast_ops import device_state
         parts = device_state(q.device).workspace(T * H * n_splits * (dv + 2))
     f = _fn("latent", "ib_latent_attention", [c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_int64,
-                                              c_int, c_int, c_int, c_int, c_int, c_float, c_int64, c_int, c_int, c_void_p, c_void_p, c_void_p])
+                                              c_int, c_int, c_int, c_int, c_int, c_float, c_int64, c_int, c_int, c_void_p, c_void_p, c_int,
+                                              c_void_p])
     _call(f, q.data_ptr(), cache.data_ptr(), block_table.data_ptr(), block_table.shape[1], step.token_seg.data_ptr(),
           step.positions.data_ptr(), out.data_ptr(), _ptr(parts), T, H, dk, int(dv), page_size, int(window or 0), float(scale),
-          n_pages, n_splits, dtype_code(q.dtype), _ptr(step.status), step.seg_start.data_ptr() if single_only else None, _stream())
+          n_pages, n_splits, dtype_code(q.dtype), _ptr(step.status), step.seg_start.data_ptr() if single_only else None, chunk,
+          _stream())
     return out
 
 

@@ -218,11 +218,10 @@ def test_bfloat16_generation_with_graphs_picks_the_maximum_up_to_rounding():
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_trace_program_on_a_model_folder(tmp_path, dtype):
-    from infer_b200.weights import write_random_model
     name = "a"
     cfg = PC.CASES[name]
     model = tmp_path / "model"
-    write_random_model(str(model), cfg, SEED, torch.bfloat16)
+    PC.write_model(str(model), cfg, SEED)
     lengths = [70, 40, 100, 33, 64]
     ids = {f"r{i}": PC.random_ids(cfg, n, 600 + i) for i, n in enumerate(lengths)}
     steps = H.trace_mixed({rid: (t, max(2, len(t) - 20)) for rid, t in ids.items()}, 256, seed=3)
@@ -244,10 +243,9 @@ def test_trace_program_on_a_model_folder(tmp_path, dtype):
 
 
 def test_generate_program_on_a_model_folder_and_on_a_preset(tmp_path):
-    from infer_b200.weights import write_random_model
     cfg = PC.CASES["a"]
     model = tmp_path / "model"
-    write_random_model(str(model), cfg, SEED, torch.bfloat16)
+    PC.write_model(str(model), cfg, SEED)
     prompt = PC.random_ids(cfg, 21, 1)
     want = pp.greedy(cfg, H.as_compute(PC.make_weights(cfg, SEED), torch.float32), prompt, 10)
     gen = os.path.join(ROOT, "bin", "generate")
