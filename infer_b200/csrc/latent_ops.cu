@@ -727,6 +727,54 @@ latent_attention_merge_kernel(const float* __restrict__ parts, const int* __rest
     }
 }
 
+// The merge after the tensor-core kernel. One CTA per (token, head). The parts' maxima give one common maximum M; part
+// i then weighs exp(m_i - M), computed once per part; the sums of a channel run over the parts in ascending order with
+// independent loads, so many are in flight. `ws` holds n_splits weights in shared memory.
+template <typename T>
+__global__ void __launch_bounds__(MG_THREADS)
+latent_attention_merge_flat_kernel(const float* __restrict__ parts, const int* __restrict__ positions, T* __restrict__ out,
+                                   int n_heads, int dv, int window, int n_splits, int chunk, const int* __restrict__ token_seg,
+                                   const int* __restrict__ seg_start) {
+    ib::pdl_wait();
+    extern __shared__ float ws[];                        // [n_splits] weights, then [dv] sums
+    __shared__ float red[32];
+    __shared__ float total;
+    const int64_t r = blockIdx.x;
+    const int64_t t = r / n_heads;
+    if (seg_start) {
+        const int sg = token_seg[t];
+        if (seg_start[sg + 1] - seg_start[sg] != 1) return;
+    }
+    const int pos = positions[t];
+    const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+    const int n = min(n_splits, pos / chunk - lo / chunk + 1);
+    const int stride = dv + 2;
+    const float* mine = parts + r * n_splits * int64_t(stride);
+    float m = -INFINITY;
+    for (int i = threadIdx.x; i < n; i += MG_THREADS) m = fmaxf(m, mine[i * int64_t(stride)]);
+    const float M = ib::block_max(m, red);
+    for (int i = threadIdx.x; i < n; i += MG_THREADS) {
+        const float mi = mine[i * int64_t(stride)];
+        ws[i] = mi == -INFINITY ? 0.0f : expf(mi - M);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float L = 0.0f;
+        for (int i = 0; i < n; i++) L = fmaf(mine[i * int64_t(stride) + 1], ws[i], L);
+        total = L;
+    }
+    for (int c = threadIdx.x; c < dv; c += MG_THREADS) {
+        float O = 0.0f;
+#pragma unroll 8
+        for (int i = 0; i < n; i++) O = fmaf(mine[i * int64_t(stride) + 2 + c], ws[i], O);
+        ws[n_splits + c] = O;                            // kept until the sum of the weights is known
+    }
+    __syncthreads();
+    const float L = total;
+    const float inv = L > 0.0f ? 1.0f / L : 0.0f;
+    for (int c = threadIdx.x; c < dv; c += MG_THREADS) out[r * dv + c] = ib::from_f32<T>(ws[n_splits + c] * inv);
+}
+
 // ------------------------------------------------------------------------------------------------
 // A head's value up-projection on its latent context, the head's gate and a constant:
 //   out[t, h * dv + e] = mult * sigmoid(gates[t, gate_col + h]) * sum_r ctx[t, h, r] * w_uvT[h, r, e]
@@ -1005,8 +1053,11 @@ IB_EXPORT int ib_latent_attention(const void* q, const void* cache, const int* b
 #undef IB_TC
         const int64_t n_rows = n_tokens * n_heads;
         if (n_rows > 0x7fffffff) return ib::fail(IB_ERR_ARG, "ib_latent_attention: too many rows to merge");
-        IB_LAUNCH(latent_attention_merge_kernel<bf16>, unsigned(n_rows), MG_THREADS, 0, parts, positions, (bf16*)out, n_heads, dv, window,
-                  n_splits, chunk, token_seg, single_start);
+        const size_t merge_smem = size_t(n_splits + dv) * sizeof(float);
+        const int rc = allow_smem(latent_attention_merge_flat_kernel<bf16>, merge_smem);
+        if (rc) return rc;
+        IB_LAUNCH(latent_attention_merge_flat_kernel<bf16>, unsigned(n_rows), MG_THREADS, merge_smem, parts, positions, (bf16*)out, n_heads,
+                  dv, window, n_splits, chunk, token_seg, single_start);
         return ib::check_launch("ib_latent_attention");
     }
     const int group = n_heads < GMAX ? n_heads : GMAX;
