@@ -727,11 +727,13 @@ latent_attention_merge_kernel(const float* __restrict__ parts, const int* __rest
     }
 }
 
-// The merge after the tensor-core kernel. One CTA per (token, head). The parts' maxima give one common maximum M; part
+constexpr int MG_FLAT_MAX = 512;
+
+// The merge after the tensor-core kernel. One CTA per (token, head), a thread per channel (up to MG_FLAT_MAX). The parts' maxima give one common maximum M; part
 // i then weighs exp(m_i - M), computed once per part; the sums of a channel run over the parts in ascending order with
 // independent loads, so many are in flight. `ws` holds n_splits weights in shared memory.
 template <typename T>
-__global__ void __launch_bounds__(MG_THREADS)
+__global__ void __launch_bounds__(MG_FLAT_MAX)
 latent_attention_merge_flat_kernel(const float* __restrict__ parts, const int* __restrict__ positions, T* __restrict__ out,
                                    int n_heads, int dv, int window, int n_splits, int chunk, const int* __restrict__ token_seg,
                                    const int* __restrict__ seg_start) {
@@ -751,9 +753,9 @@ latent_attention_merge_flat_kernel(const float* __restrict__ parts, const int* _
     const int stride = dv + 2;
     const float* mine = parts + r * n_splits * int64_t(stride);
     float m = -INFINITY;
-    for (int i = threadIdx.x; i < n; i += MG_THREADS) m = fmaxf(m, mine[i * int64_t(stride)]);
+    for (int i = threadIdx.x; i < n; i += blockDim.x) m = fmaxf(m, mine[i * int64_t(stride)]);
     const float M = ib::block_max(m, red);
-    for (int i = threadIdx.x; i < n; i += MG_THREADS) {
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
         const float mi = mine[i * int64_t(stride)];
         ws[i] = mi == -INFINITY ? 0.0f : expf(mi - M);
     }
@@ -763,7 +765,7 @@ latent_attention_merge_flat_kernel(const float* __restrict__ parts, const int* _
         for (int i = 0; i < n; i++) L = fmaf(mine[i * int64_t(stride) + 1], ws[i], L);
         total = L;
     }
-    for (int c = threadIdx.x; c < dv; c += MG_THREADS) {
+    for (int c = threadIdx.x; c < dv; c += blockDim.x) {
         float O = 0.0f;
 #pragma unroll 8
         for (int i = 0; i < n; i++) O = fmaf(mine[i * int64_t(stride) + 2 + c], ws[i], O);
@@ -772,7 +774,7 @@ latent_attention_merge_flat_kernel(const float* __restrict__ parts, const int* _
     __syncthreads();
     const float L = total;
     const float inv = L > 0.0f ? 1.0f / L : 0.0f;
-    for (int c = threadIdx.x; c < dv; c += MG_THREADS) out[r * dv + c] = ib::from_f32<T>(ws[n_splits + c] * inv);
+    for (int c = threadIdx.x; c < dv; c += blockDim.x) out[r * dv + c] = ib::from_f32<T>(ws[n_splits + c] * inv);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -1056,7 +1058,8 @@ IB_EXPORT int ib_latent_attention(const void* q, const void* cache, const int* b
         const size_t merge_smem = size_t(n_splits + dv) * sizeof(float);
         const int rc = allow_smem(latent_attention_merge_flat_kernel<bf16>, merge_smem);
         if (rc) return rc;
-        IB_LAUNCH(latent_attention_merge_flat_kernel<bf16>, unsigned(n_rows), MG_THREADS, merge_smem, parts, positions, (bf16*)out, n_heads,
+        const int merge_threads = dv >= MG_FLAT_MAX ? MG_FLAT_MAX : dv <= MG_THREADS ? MG_THREADS : (dv + 31) / 32 * 32;
+        IB_LAUNCH(latent_attention_merge_flat_kernel<bf16>, unsigned(n_rows), merge_threads, merge_smem, parts, positions, (bf16*)out, n_heads,
                   dv, window, n_splits, chunk, token_seg, single_start);
         return ib::check_launch("ib_latent_attention");
     }
