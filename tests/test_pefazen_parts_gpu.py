@@ -25,7 +25,7 @@ def test_layer_norm_against_the_plain_one():
     for rows, width in ((5, 36), (33, 128), (2, 1000)):
         x = (torch.randn(rows, width, generator=g) * 3 + 1.5)
         w = 1 + 0.2 * torch.randn(width, generator=g)
-        want = pp.layer_norm(x, w, 3e-6)
+        want = pp.layer_norm(x.double(), w.double(), 3e-6).float()
         got = ops.layer_norm(x.to(DEV), w.to(DEV), 3e-6, torch.float32).cpu()
         assert torch.allclose(got, want, atol=2e-5, rtol=1e-5)
         got16 = ops.layer_norm(x.to(DEV), w.to(DEV), 3e-6, torch.bfloat16).float().cpu()
@@ -39,8 +39,8 @@ def test_sigmoid_router_against_the_plain_choice(experts, top):
     h = torch.randn(40, 24, generator=g)
     Wr = 0.4 * torch.randn(experts, 24, generator=g)
     corr = 0.3 * torch.randn(experts, generator=g)
-    chosen, weights = pp.choose_experts(h, Wr, corr, top)[:2]
-    logits = pp.linear(h, Wr).float()
+    chosen, weights = pp.choose_experts(h.double(), Wr, corr, top)[:2]
+    logits = pp.linear(h.double(), Wr).float()
     w_got, c_got = ops.route_sigmoid(logits.to(DEV), corr.to(DEV), top, 0.5, want_chosen=True)
     w_got, c_got = w_got.cpu(), c_got.cpu()
     for t in range(h.shape[0]):
@@ -66,11 +66,11 @@ def test_relu_squared_with_weights_and_capped_logits(dtype):
     g = _gen(3)
     x = torch.randn(7, 5 * 24, generator=g).to(dtype)
     scale = torch.rand(7, 5, generator=g)
-    want = pp.relu_squared(x.float()) * scale.repeat_interleave(24, dim=1)
+    want = (pp.relu_squared(x.double()) * scale.double().repeat_interleave(24, dim=1)).float()
     got = ops.scaled_relu_sq(x.to(DEV), scale.to(DEV), 24).float().cpu()
     assert torch.allclose(got, want, atol=1e-6 if dtype == torch.float32 else 0.02, rtol=1e-6 if dtype == torch.float32 else 0.01)
     z = 20 * torch.randn(3, 50, generator=g)
-    want = pp.soft_cap(z * 0.7, 12.0)
+    want = pp.soft_cap(z.double() * 0.7, 12.0).float()
     assert torch.allclose(ops.scale_softcap(z.clone().to(DEV), 0.7, 12.0).cpu(), want, atol=1e-5)
     assert torch.allclose(ops.scale_softcap(z.clone().to(DEV), 0.7, 0.0).cpu(), z * 0.7, atol=1e-6)
 
@@ -195,7 +195,7 @@ def test_portions_with_per_head_keys_and_values(layout, window, heads, d, dr, dv
         region0 = max(0, pos0[s] - window + 1) if window else 0
         base = portions.index(s) * span - region0
         qt = q[t].float().view(heads, d + dr).double()
-        qr = pp.rotate(qt[:, d:d + n_rot].float(), torch.tensor([pos]), freq, layout).double().view(heads, n_rot)
+        qr = pp.rotate(qt[:, d:d + n_rot], torch.tensor([pos]), freq, layout).double().view(heads, n_rot)
         for h in range(heads):
             keys_c = rows[s][lo:pos + 1].double()
             k_plain = kvs[base + lo:base + pos + 1, h * d:(h + 1) * d].double()
