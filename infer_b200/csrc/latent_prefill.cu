@@ -326,8 +326,24 @@ latent_prefill_kernel(const bf16* __restrict__ q, const float* __restrict__ cos_
                 split2(sc[2 * kk][2], sc[2 * kk][3], ph[1], pl[1]);
                 split2(sc[2 * kk + 1][0], sc[2 * kk + 1][1], ph[2], pl[2]);
                 split2(sc[2 * kk + 1][2], sc[2 * kk + 1][3], ph[3], pl[3]);
+                // two channel tiles at a time: four products lie between the two that add into one accumulator
 #pragma unroll
-                for (int np = 0; np < DV / 16; np++) {
+                for (int np = 0; np + 1 < DV / 16; np += 2) {
+                    uint32_t b[4], c[4];
+                    const uint32_t at = smem_u32(Vs + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * VS + np * 16 + (lane >> 4) * 8);
+                    ldsm4_t(at, b);
+                    ldsm4_t(at + 32, c);
+                    mma16816(o[2 * np], ph, b[0], b[1]);
+                    mma16816(o[2 * np + 1], ph, b[2], b[3]);
+                    mma16816(o[2 * np + 2], ph, c[0], c[1]);
+                    mma16816(o[2 * np + 3], ph, c[2], c[3]);
+                    mma16816(o[2 * np], pl, b[0], b[1]);
+                    mma16816(o[2 * np + 1], pl, b[2], b[3]);
+                    mma16816(o[2 * np + 2], pl, c[0], c[1]);
+                    mma16816(o[2 * np + 3], pl, c[2], c[3]);
+                }
+                if ((DV / 16) % 2) {
+                    constexpr int np = DV / 16 - 1;
                     uint32_t b[4];
                     ldsm4_t(smem_u32(Vs + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * VS + np * 16 + (lane >> 4) * 8), b);
                     mma16816(o[2 * np], ph, b[0], b[1]);

@@ -957,11 +957,12 @@ def latent_portion_build(d: int, dr: int, dv: int, kv_rank: int):
 
 
 def latent_gather(cache: torch.Tensor, block_table: torch.Tensor, step, n_portions: int, span: int, window: Optional[int],
-                  kv_rank: int):
+                  kv_rank: int, defines=None):
     """The rows that the step's portions (segments longer than one token, in order) can see, out of the pages
     ``cache`` [pages, page_size, kv_rank + dr] into one region of ``span`` rows per portion: row j of a region is
     position lo + j, lo = max(0, first position of the portion - window + 1) (0 without a window); rows past the
-    portion's last token are zero. Returns (c [portions * span, kv_rank], r [portions * span, dr])."""
+    portion's last token are zero. Returns (c [portions * span, kv_rank], r [portions * span, dr]). ``defines``: the
+    build of the module to take the kernel from (the one the portion kernel of these sizes uses)."""
     _check(cache, "cache", torch.bfloat16)
     n_pages, page_size, dk = cache.shape
     dr = dk - kv_rank
@@ -970,7 +971,7 @@ def latent_gather(cache: torch.Tensor, block_table: torch.Tensor, step, n_portio
     c = torch.empty((n, kv_rank), dtype=cache.dtype, device=cache.device)
     r = torch.empty((n, dr), dtype=cache.dtype, device=cache.device)
     f = _fn("latent_pf", "ib_latent_gather", [c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int64,
-                                              c_int, c_int, c_void_p, c_void_p, c_int64, c_void_p, c_void_p])
+                                              c_int, c_int, c_void_p, c_void_p, c_int64, c_void_p, c_void_p], defines)
     _call(f, cache.data_ptr(), block_table.data_ptr(), block_table.shape[1], step.seg_start.data_ptr(), step.seg_pos0.data_ptr(),
           step.n_segments, int(span), int(window or 0), page_size, n_pages, int(kv_rank), dr, c.data_ptr(), r.data_ptr(), n,
           _ptr(step.status), _stream())

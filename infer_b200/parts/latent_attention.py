@@ -191,7 +191,7 @@ class LatentAttention(Mixer):
         if span:
             # portions: per-head keys and values of the rows they can see, ordinary attention on the tensor cores
             n_portions = sum(1 for n in step.seg_lens if n > 1)
-            c_rows, r_rows = ops.latent_gather(pages, table, step, n_portions, span, self.window, self.kv_rank)
+            c_rows, r_rows = ops.latent_gather(pages, table, step, n_portions, span, self.window, self.kv_rank, self.portion_build)
             kv = self.up_kv(c_rows)
             heads = ops.latent_prefill(q, cos, sin, layout, kv, self.n_heads * self.head_dim, r_rows, gates, self.gate_col, self.out_scale,
                                        step, span, self.n_heads, self.head_dim, self.rot_dim, self.v_dim, self.window, self.scale,

@@ -175,7 +175,7 @@ def test_portions_with_per_head_keys_and_values(layout, window, heads, d, dr, dv
     cos, sin = ang.cos().float(), ang.sin().float()
     portions = [i for i, n in enumerate(seg_lens) if n > 1]
     span = table.shape[1] * 16 if window is None else min(table.shape[1] * 16, window - 1 + max(seg_lens))
-    c_rows, r_rows = ops.latent_gather(cache, table, step, len(portions), span, window, R)
+    c_rows, r_rows = ops.latent_gather(cache, table, step, len(portions), span, window, R, defines)
     assert torch.isfinite(c_rows.float()).all() and torch.isfinite(r_rows.float()).all()
     kv = (c_rows.float() @ w_kv.float().to(DEV).T).to(torch.bfloat16)
     out = torch.full((T, heads * dv), 7.0, dtype=torch.bfloat16, device=DEV)
