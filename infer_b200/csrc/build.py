@@ -41,7 +41,7 @@ MODULES: Dict[str, str] = {
 }
 HEADERS = ["common.cuh", "gemm_static.h", "tma_map.cuh"]
 # modules that are compiled per model size: the variant that build_all() makes (others are built at first use)
-DEFAULT_DEFINES = {"attn": {"IB_HEAD_DIM": 128}, "attn_tc": {"IB_HEAD_DIM": 128}, "latent_pf": {"IB_QK_DIM": 192, "IB_V_DIM": 128}}
+DEFAULT_DEFINES = {"attn": {"IB_HEAD_DIM": 128}, "attn_tc": {"IB_HEAD_DIM": 128}, "latent_pf": {"IB_QK_DIM": 128, "IB_V_DIM": 128}}
 
 
 class BuildError(RuntimeError):
