@@ -13,7 +13,9 @@
 //   latent_attention  paged attention of H query heads over the one row per position; values are the first kv_rank
 //                     channels of the key row; window optional; keys in chunks of 128 aligned to absolute positions,
 //                     chunk results merged in ascending order (in the CTA, or by latent_attention_merge when a
-//                     decode step spreads a token's chunks over CTAs; the arithmetic is the same, so the bits are)
+//                     decode step spreads a token's chunks over CTAs; the arithmetic is the same, so the bits are);
+//                     for single tokens in bfloat16 a tensor-core form: a token's heads are the rows of mma.sync
+//                     tiles over chunks of 64 keys held in shared memory (latent_attention_tc, merge_flat)
 //   latent_output     per (token, head): W_uv_h applied to the latent context, times sigmoid(gate) and a constant
 //   route_sigmoid     router with sigmoid scores, a correction that only the choice sees, weights not renormalised
 //   scaled_relu_sq    hidden layer of ungated experts: relu(x)^2 times the token's weight for the expert

@@ -878,9 +878,12 @@ LATENT_PARTS_MAX_BYTES = 512 << 20
 def latent_attention(q: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor, step, dv: int, window: Optional[int],
                      scale: float, split: Optional[bool] = None, single_only: bool = False) -> torch.Tensor:
     """q [T, heads, dk] over the rows ``cache`` [pages, page_size, dk] -> contexts [T, heads, dv]: a row's first dv
-    channels are its value. ``split``: spread a token's key chunks over CTAs (default: in steps of single tokens that
-    alone would not fill the device); the result's bits do not depend on it. With ``single_only`` only tokens that are
-    a segment of their own are computed (the other rows of the result are not written)."""
+    channels are its value. Two kernels. A thread per key, chunks of 128 keys, float32 or bfloat16: ``split`` spreads
+    a token's chunks over CTAs (default: in steps of single tokens that alone would not fill the device); the
+    result's bits do not depend on it. In bfloat16, steps of single tokens (and the single tokens of a mixed step,
+    with ``single_only``) take chunks of 64 keys on the tensor cores, always spread over CTAs (``split=False`` keeps
+    them on the first kernel); the two kernels differ by rounding. With ``single_only`` only tokens that are a
+    segment of their own are computed (the other rows of the result are not written)."""
     _check(q, "q")
     T, H, dk = q.shape
     n_pages, page_size, _ = cache.shape
