@@ -165,6 +165,37 @@ def test_a_batch_of_unequal_requests_equals_each_alone():
             assert np.array_equal(alone[r][p], together[r][p])
 
 
+def test_a_captured_portion_shape_replays_at_other_start_positions_and_beside_single_tokens():
+    """What a captured step froze on the host may depend on the segments' lengths and the tables' widths only: the
+    same shape (a portion of 24 tokens, alone and beside another request's single token) is replayed at other context
+    starts, across the windows' edges, and gives the bits of the eager engine (which the tests above hold against the
+    plain implementation)."""
+    from infer_b200.engine import StepEntry
+    name = "a"
+    cfg = PC.CASES[name]
+    eager = _engine(name, torch.bfloat16, cuda_graphs=False)
+    graph = _engine(name, torch.bfloat16)
+    starts = [0, 0, 0, 7, 50, 90, 3, 33]
+    for r, start in enumerate(starts):
+        ids = PC.random_ids(cfg, start + 25, 300 + r)
+        other = PC.random_ids(cfg, 11, 400 + r)
+        outs = []
+        for eng in (eager, graph):
+            eng.add_request("x")
+            eng.add_request("y")
+            eng.step([StepEntry("y", other[:10], [])])
+            if start:
+                eng.step([StepEntry("x", ids[:start], [])])
+            a = eng.step([StepEntry("x", ids[start:start + 24], [0, 23])]).float().cpu()
+            b = eng.step([StepEntry("y", other[10:], [0]), StepEntry("x", ids[start + 24:], [0])]).float().cpu()
+            eng.check_status()
+            eng.end_request("x")
+            eng.end_request("y")
+            outs.append(torch.cat([a, b]))
+        assert torch.equal(outs[0], outs[1]), f"start {start}"
+    assert any(k[0] == "portions" and len(graph._graphs[k].graphs) == 1 for k in graph._graphs), list(graph._graphs)
+
+
 def test_the_design_runs_on_its_own_kernels():
     from infer_b200 import ops
     eng = _engine("c", torch.bfloat16)
