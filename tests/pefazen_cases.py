@@ -58,6 +58,15 @@ CASES: Dict[str, dict] = {
           "layers": [{"type": W1, "mixer": _mix(12, 64, 32, 48, 96, 192, 0.1, 20000.0, window=80, dims=24), "mlp": _moe(8, 2, 32)},
                      {"type": W2, "mixer": _mix(4, 32, 16, 80, 64, 264, 0.12, 1000000.0, scaling=(2.0, 2048, 32.0, 1.0)), "mlp": _moe(16, 4, 16)},
                      {"type": W1, "mixer": _mix(2, 128, 32, 128, 72, 192, 0.08, 20000.0, window=130, kv_from=0, dims=24), "mlp": None}]},
+    # sizes that are multiples of eight throughout (the tensor-core forms in bfloat16): eighteen heads (two groups of
+    # sixteen), a reader of a layer that sees everything, values of 136 (beyond what the portion kernel takes: portions
+    # stay in the latent form there, single tokens do not), windows of 70 and of exactly one key tile
+    "d": {"architecture": "Pefazen", "vocab": 160, "width": 96, "norm": {"eps": 1e-5}, "residual_mult": 0.7, "logit_scale": 1.5,
+          "logit_softcap": 8.0,
+          "layers": [{"type": W2, "mixer": _mix(18, 16, 16, 16, 48, 64, 0.2, 5000.0, scaling=(3.0, 128, 4.0, 0.5)), "mlp": _moe(4, 1, 24)},
+                     {"type": W2, "mixer": _mix(2, 24, 16, 136, 40, 64, 0.15, 5000.0, kv_from=0, scaling=(3.0, 128, 4.0, 0.5)), "mlp": None},
+                     {"type": W1, "mixer": _mix(4, 8, 8, 40, 24, 72, 0.3, 300.0, window=70), "mlp": _moe(3, 3, 16)},
+                     {"type": W1, "mixer": _mix(3, 32, 8, 8, 32, 72, 0.25, 300.0, window=64, kv_from=2), "mlp": _moe(8, 2, 8)}]},
 }
 
 

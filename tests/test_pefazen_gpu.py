@@ -31,7 +31,7 @@ def _requests(name, lengths, seed0=0):
 
 
 @pytest.mark.parametrize("dtype", DTYPES, ids=["f32", "bf16"])
-@pytest.mark.parametrize("name", ["a", "b", "c"])
+@pytest.mark.parametrize("name", ["a", "b", "c", "d"])
 def test_whole(name, dtype):
     reqs = _requests(name, [5, 17, 33, 90, 1, 2, 170])
     eng = _engine(name, dtype)
@@ -41,7 +41,7 @@ def test_whole(name, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES, ids=["f32", "bf16"])
-@pytest.mark.parametrize("name", ["a", "b", "c"])
+@pytest.mark.parametrize("name", ["a", "b", "c", "d"])
 def test_tail_one_by_one(name, dtype):
     """The last 40 tokens decoded one by one: windows of 1, 5, 9, 24 and 33 pass over decoded tokens."""
     reqs = _requests(name, [110, 47], seed0=10)
@@ -50,7 +50,7 @@ def test_tail_one_by_one(name, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES, ids=["f32", "bf16"])
-@pytest.mark.parametrize("name", ["a", "b", "c"])
+@pytest.mark.parametrize("name", ["a", "b", "c", "d"])
 def test_portions_of_changing_size(name, dtype):
     reqs = _requests(name, [150, 61], seed0=20)
     got = H.run_trace(_engine(name, dtype), H.trace_portions(reqs))
@@ -58,7 +58,7 @@ def test_portions_of_changing_size(name, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES, ids=["f32", "bf16"])
-@pytest.mark.parametrize("name", ["a", "b"])
+@pytest.mark.parametrize("name", ["a", "b", "d"])
 def test_mixed_with_pages_and_slots_used_again(name, dtype):
     lengths = [60, 45, 100, 33, 64, 90, 20, 77]
     ids = _requests(name, lengths, seed0=30)
