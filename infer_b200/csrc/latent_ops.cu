@@ -566,26 +566,36 @@ latent_attention_tc_kernel(const bf16* __restrict__ q, const bf16* __restrict__ 
     bf16* Pl = Ph + TC_HEADS * TC_PS;                        // [16][TC_PS]
     float* red = reinterpret_cast<float*>(Pl + TC_HEADS * TC_PS);   // [2][4][16] maxima, sums
     const int* table = block_table + int64_t(token_seg[t]) * max_blocks;
-    const int cpr = dkp / 8, base = ch * TC_KC;
-    for (int i = tid; i < TC_KC * cpr; i += TC_THREADS) {
-        const int row = i / cpr, e = (i - row * cpr) * 8, key = base + row;
-        const bf16* src = cache;
-        int bytes = 0;
-        if (key >= lo && key <= pos && e < dk) {
+    const int cpr = dkp / 8, real = dk / 8, base = ch * TC_KC;
+    {
+        // two threads per key row: one page lookup per thread, then every other 16-byte piece of the row
+        static_assert(TC_THREADS == 2 * TC_KC, "two threads per key row");
+        const int row = tid >> 1, key = base + row;
+        const bf16* src = nullptr;
+        if (key >= lo && key <= pos) {
             const int page = table[key / page_size];
             if (page < 0 || page >= n_pages) {
                 if (status) atomicExch(status, 3);
             } else {
-                src = cache + (int64_t(page) * page_size + key % page_size) * dk + e;
-                bytes = 16;
+                src = cache + (int64_t(page) * page_size + key % page_size) * dk;
             }
         }
-        cp_async16(smem_u32(Ks + row * RS + e), src, bytes);
+        const uint32_t dst = smem_u32(Ks + row * RS);
+        for (int c = tid & 1; c < cpr; c += 2) {
+            const bool on = src && c < real;
+            cp_async16(dst + c * 16, on ? src + c * 8 : cache, on ? 16 : 0);
+        }
     }
-    for (int i = tid; i < TC_HEADS * cpr; i += TC_THREADS) {
-        const int row = i / cpr, e = (i - row * cpr) * 8;
-        const bool on = row < ng && e < dk;
-        cp_async16(smem_u32(Qs + row * RS + e), on ? q + (t * n_heads + h0 + row) * dk + e : q, on ? 16 : 0);
+    {
+        // eight threads per head row of the queries
+        static_assert(TC_THREADS == 8 * TC_HEADS, "eight threads per query row");
+        const int row = tid >> 3;
+        const bf16* src = row < ng ? q + (t * n_heads + h0 + row) * dk : nullptr;
+        const uint32_t dst = smem_u32(Qs + row * RS);
+        for (int c = tid & 7; c < cpr; c += 8) {
+            const bool on = src && c < real;
+            cp_async16(dst + c * 16, on ? src + c * 8 : q, on ? 16 : 0);
+        }
     }
     cp_async_wait_all();
     __syncthreads();
@@ -680,8 +690,12 @@ latent_attention_tc_kernel(const bf16* __restrict__ q, const bf16* __restrict__ 
 #pragma unroll
         for (int i = 0; i < 2 * NV; i++) {
             const int col = c0 + i * 8 + (lane & 3) * 2;
-            if (col < dv) dst[2 + col] = o[i][2 * half_i];
-            if (col + 1 < dv) dst[2 + col + 1] = o[i][2 * half_i + 1];
+            if (col + 1 < dv && !(dv & 1)) {                // an even dv keeps every pair on an 8-byte boundary
+                *reinterpret_cast<float2*>(dst + 2 + col) = make_float2(o[i][2 * half_i], o[i][2 * half_i + 1]);
+            } else {
+                if (col < dv) dst[2 + col] = o[i][2 * half_i];
+                if (col + 1 < dv) dst[2 + col + 1] = o[i][2 * half_i + 1];
+            }
         }
     }
 }
@@ -740,9 +754,8 @@ latent_attention_merge_flat_kernel(const float* __restrict__ parts, const int* _
                                    int n_heads, int dv, int window, int n_splits, int chunk, const int* __restrict__ token_seg,
                                    const int* __restrict__ seg_start) {
     ib::pdl_wait();
-    extern __shared__ float ws[];                        // [n_splits] weights, then [dv] sums
+    extern __shared__ float ws[];                        // [n_splits] weights, then [n_splits] the parts' sums
     __shared__ float red[32];
-    __shared__ float total;
     const int64_t r = blockIdx.x;
     const int64_t t = r / n_heads;
     if (seg_start) {
@@ -754,29 +767,27 @@ latent_attention_merge_flat_kernel(const float* __restrict__ parts, const int* _
     const int n = min(n_splits, pos / chunk - lo / chunk + 1);
     const int stride = dv + 2;
     const float* mine = parts + r * n_splits * int64_t(stride);
+    float* ls = ws + n_splits;
     float m = -INFINITY;
-    for (int i = threadIdx.x; i < n; i += blockDim.x) m = fmaxf(m, mine[i * int64_t(stride)]);
-    const float M = ib::block_max(m, red);
     for (int i = threadIdx.x; i < n; i += blockDim.x) {
-        const float mi = mine[i * int64_t(stride)];
-        ws[i] = mi == -INFINITY ? 0.0f : expf(mi - M);
+        const float2 ml = *reinterpret_cast<const float2*>(mine + i * int64_t(stride));   // rows start on 8 bytes: dv is even
+        ws[i] = ml.x;
+        ls[i] = ml.y;
+        m = fmaxf(m, ml.x);
     }
+    const float M = ib::block_max(m, red);
+    for (int i = threadIdx.x; i < n; i += blockDim.x) ws[i] = ws[i] == -INFINITY ? 0.0f : expf(ws[i] - M);
     __syncthreads();
-    if (threadIdx.x == 0) {
-        float L = 0.0f;
-        for (int i = 0; i < n; i++) L = fmaf(mine[i * int64_t(stride) + 1], ws[i], L);
-        total = L;
-    }
+    float L = 0.0f;                                      // every thread adds the same terms in the same order
+#pragma unroll 8
+    for (int i = 0; i < n; i++) L = fmaf(ls[i], ws[i], L);
+    const float inv = L > 0.0f ? 1.0f / L : 0.0f;
     for (int c = threadIdx.x; c < dv; c += blockDim.x) {
         float O = 0.0f;
 #pragma unroll 8
         for (int i = 0; i < n; i++) O = fmaf(mine[i * int64_t(stride) + 2 + c], ws[i], O);
-        ws[n_splits + c] = O;                            // kept until the sum of the weights is known
+        out[r * dv + c] = ib::from_f32<T>(O * inv);
     }
-    __syncthreads();
-    const float L = total;
-    const float inv = L > 0.0f ? 1.0f / L : 0.0f;
-    for (int c = threadIdx.x; c < dv; c += blockDim.x) out[r * dv + c] = ib::from_f32<T>(ws[n_splits + c] * inv);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -1040,8 +1051,8 @@ IB_EXPORT int ib_latent_attention(const void* q, const void* cache, const int* b
     if (n_splits > 65535 || (n_heads + GMAX - 1) / GMAX > 65535) return ib::fail(IB_ERR_ARG, "ib_latent_attention: grid too large");
     if (chunk == TC_KC) {
         // chunks of 64 keys: the tensor-core kernel, which always leaves parts for the merge
-        if (dtype != IB_BF16 || dk % 8 || dv > 512 || !parts)
-            return ib::fail(IB_ERR_ARG, "ib_latent_attention: the tensor-core kernel takes bfloat16 rows of a multiple of 8 channels, values up to 512 and a workspace");
+        if (dtype != IB_BF16 || dk % 8 || dv % 2 || dv > 512 || !parts)
+            return ib::fail(IB_ERR_ARG, "ib_latent_attention: the tensor-core kernel takes bfloat16 rows of a multiple of 8 channels, an even number of values up to 512 and a workspace");
         const int nv = dv <= 64 ? 1 : dv <= 128 ? 2 : dv <= 256 ? 4 : 8;
         const int RS = tc_row_stride(dk);
         const size_t smem = (size_t(TC_HEADS + TC_KC) * RS + 64 * nv + 2 * TC_HEADS * TC_PS) * sizeof(bf16) + 128 * sizeof(float);
@@ -1057,7 +1068,7 @@ IB_EXPORT int ib_latent_attention(const void* q, const void* cache, const int* b
 #undef IB_TC
         const int64_t n_rows = n_tokens * n_heads;
         if (n_rows > 0x7fffffff) return ib::fail(IB_ERR_ARG, "ib_latent_attention: too many rows to merge");
-        const size_t merge_smem = size_t(n_splits + dv) * sizeof(float);
+        const size_t merge_smem = size_t(2 * n_splits) * sizeof(float);
         const int rc = allow_smem(latent_attention_merge_flat_kernel<bf16>, merge_smem);
         if (rc) return rc;
         const int merge_threads = dv >= MG_FLAT_MAX ? MG_FLAT_MAX : dv <= MG_THREADS ? MG_THREADS : (dv + 31) / 32 * 32;

@@ -892,7 +892,7 @@ def latent_attention(q: torch.Tensor, cache: torch.Tensor, block_table: torch.Te
     singles = T if step.decode_only else sum(1 for n in step.seg_lens if n == 1)
     # single tokens in bfloat16: chunks of 64 keys on the tensor cores, always spread over CTAs (while the parts fit)
     chunk = LATENT_CHUNK
-    if q.dtype == torch.bfloat16 and dk % 8 == 0 and dv <= 512 and (step.decode_only or single_only) and split is not False:
+    if q.dtype == torch.bfloat16 and dk % 8 == 0 and dv % 2 == 0 and dv <= 512 and (step.decode_only or single_only) and split is not False:
         chunk = LATENT_CHUNK_TC
     span = step.max_ctx_len if not window else min(step.max_ctx_len, int(window) + chunk - 1)
     chunks = max(1, -(-span // chunk) + (1 if window else 0))
