@@ -10,7 +10,8 @@ Paged entries with the same (kv heads, key and value size, window) form a *group
 pool and one block table per request, and a page id addresses the same page in every entry of the
 group (the reference has one implicit group: one block id spans all layers,
 kernels/batch_gpu.cu:75,114-118).  Groups with a window give pages back as soon as every later
-query is past them; their block tables then hold -1 at that place.
+query is past them; their block tables then hold -1 at that place.  A need with ``keep_first`` keeps the pages
+that hold the positions below it: every later query still reads those.
 
 An entry may also state a ``CompositeNeed``: several needs by name (pages AND a fixed-size state for one mixer;
 the needs of mixers that run side by side). Its leaves are placed as above, under the key (cache index, name, ...),
@@ -130,7 +131,8 @@ class CacheManager:
         def place(key, need):
             """key: the cache index, or (cache index, name, ...) for a leaf of a composite need."""
             if isinstance(need, PagedKVNeed):
-                gkey = (need.num_kv_heads, need.head_dim, need.value_dim, need.window, need.values_in_keys)
+                gkey = (need.num_kv_heads, need.head_dim, need.value_dim, need.window, need.values_in_keys,
+                        need.keep_first if need.window is not None else 0)
                 g = by_key.get(gkey)
                 if g is None:
                     g = CacheGroup(len(self.groups), need, [], PagePool(n_pages), page_size)
@@ -265,7 +267,8 @@ class CacheManager:
         rc.length += n
         for g, table in zip(self.groups, rc.tables):
             first = min(self._first_needed_page(g, rc.length), len(table))
-            for i in range(first):
+            kept = -(-g.need.keep_first // self.page_size) if g.need.keep_first > 0 else 0      # pages of the kept first positions
+            for i in range(kept, first):
                 if table[i] >= 0:
                     g.pool.free(table[i])
                     table[i] = -1

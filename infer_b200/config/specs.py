@@ -42,9 +42,11 @@ class LayerSpec:
     parts maps a slot name, which the block class defines, to (family, PartSpec), in the order in which the block
     runs them. The framework does not know the slot names: it builds, loads and binds whatever the mapping holds,
     and hands the built parts to the block class by slot name. A block with a third norm, without a feed-forward,
-    or with two mixers is another block class and another mapping, not another framework."""
+    or with two mixers is another block class and another mapping, not another framework. ``options`` are constants of
+    the arrangement itself (a multiplier on the residual stream, say); the block class takes them as keyword arguments."""
     block: str
     parts: Mapping[str, Tuple[str, PartSpec]]
+    options: Mapping[str, Any] = field(default_factory=dict)
 
     def __post_init__(self):
         for slot, fp in self.parts.items():

@@ -32,6 +32,7 @@ MODULES: Dict[str, str] = {
     "seq": "seq_ops.cu",         # filters over time, pair rotation, gated recurrence, side-by-side sublayers
     "mix": "mix_ops.cu",         # norms on sublayer results, decayed and delta-rule recurrences, routers, row norms of q and k
     "latent": "latent_ops.cu",   # attention through low-rank latents, layer norm, sigmoid router, capped logits
+    "post": "post_ops.cu",       # norms after the residual sum, per-head query/key norms, mixtures with the token before
     "latent_pf": "latent_prefill.cu",   # the same attention for prompt portions: per-head keys and values, tensor cores
     "gemvb": "gemv_bulk.cu",
     "gemm": "gemm_tcgen05.cu",

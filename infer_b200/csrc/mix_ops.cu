@@ -109,6 +109,7 @@ dual_norm_sum_kernel(const float* __restrict__ a, const float* __restrict__ wa, 
 // rows -> out [tokens, width] contiguous.
 //   kind 0: gelu_tanh(g) * u
 //   kind 1: g' = min(g, limit), u' = clamp(u, -limit, limit): g' * sigmoid(slope * g') * (u' + 1)
+//   kind 2: g * sigmoid(g) * u
 // Columns are cut into blocks of `group` (an expert's hidden size): block e of token t is multiplied by
 // scale[t * n_groups + e] (a router's weight, zero for an expert the token does not use); columns from
 // n_groups * group on (a shared expert) are not scaled and use limit2.
@@ -125,6 +126,10 @@ __global__ void glu_act_kernel(const T* __restrict__ rows, int64_t ld, int64_t g
     float y;
     if (kind == 0) {
         y = 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g))) * u;
+    } else if (kind == 2) {
+        const int64_t e = group > 0 ? c / group : 0;
+        y = silu_(g) * u;
+        if (scale && e < n_groups) y *= scale[t * n_groups + e];
     } else {
         const int64_t e = group > 0 ? c / group : 0;
         const float lim = (group > 0 && e >= n_groups) ? limit2 : limit;
@@ -151,7 +156,7 @@ __global__ void glu_act_vec_kernel(const bf16* __restrict__ rows, int64_t ld, in
     const __nv_bfloat162* uh = reinterpret_cast<const __nv_bfloat162*>(&uu);
     const int64_t e = group > 0 ? c / group : 0;
     const float lim = (group > 0 && e >= n_groups) ? limit2 : limit;
-    const float sc = (kind == 1 && scale && e < n_groups) ? scale[t * n_groups + e] : 1.0f;
+    const float sc = (kind != 0 && scale && e < n_groups) ? scale[t * n_groups + e] : 1.0f;
     uint4 res;
     __nv_bfloat162* rh = reinterpret_cast<__nv_bfloat162*>(&res);
 #pragma unroll
@@ -163,6 +168,8 @@ __global__ void glu_act_vec_kernel(const bf16* __restrict__ rows, int64_t ld, in
             float g = j ? g2.y : g2.x, u = j ? u2.y : u2.x;
             if (kind == 0) {
                 y[j] = 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g))) * u;
+            } else if (kind == 2) {
+                y[j] = silu_(g) * u * sc;
             } else {
                 g = fminf(g, lim);
                 u = fminf(fmaxf(u, -lim), lim);
@@ -305,6 +312,8 @@ rownorm_store_kernel(const T* __restrict__ rows, int64_t ld, int col0, const flo
 // A chunk leaves (maximum, sum, unnormalised context) per head in the workspace; the merge kernel adds a token's
 // chunks in ascending order, counts the sink once and divides. What a token's result depends on is (window, position)
 // only. `single_only` (a step's seg_start): tokens of longer segments are skipped (another kernel's).
+// With keep_first > 0 a windowed query also sees the keys below keep_first: their chunks come first in a token's list of
+// chunks, then the window's. With `slopes` [heads], slopes[h] * (position - key) is taken off the scaled score.
 constexpr int KC = 128;
 constexpr int GMAX = 16;
 constexpr int VT = 32;                 // value rows staged at a time
@@ -335,7 +344,8 @@ split_attention_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, c
                        const int* __restrict__ block_table, int64_t max_blocks, const int* __restrict__ token_seg,
                        const int* __restrict__ positions, const int* __restrict__ single_only, float* __restrict__ parts,
                        int n_heads, int n_kv, int d, int dv, int page_size, int window, float scale, int64_t n_pages,
-                       const float* __restrict__ dist_bias, int bias_len, int n_chunks, int vec, int vec_v, int* status) {
+                       const float* __restrict__ dist_bias, int bias_len, int n_chunks, int vec, int vec_v, int* status,
+                       int keep_first, const float* __restrict__ slopes) {
     ib::pdl_wait();
     const int64_t t = blockIdx.x;
     const int g = blockIdx.y, ci = blockIdx.z, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -343,7 +353,9 @@ split_attention_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, c
     if (single_only && single_only[sg + 1] - single_only[sg] > 1) return;
     const int pos = positions[t];
     const int lo = window > 0 ? max(0, pos - window + 1) : 0;
-    const int base = (lo / KC + ci) * KC;
+    const int keep_end = min(keep_first, lo);                    // keys below it are seen although the window has passed
+    const int nk = min((keep_end + KC - 1) / KC, lo / KC);      // chunks of kept keys that lie wholly before the window's first
+    const int base = ci < nk ? ci * KC : (lo / KC + ci - nk) * KC;
     if (base > pos) return;
     const int group = n_heads / n_kv, h0 = g * group;
     extern __shared__ __align__(16) float sm[];
@@ -359,12 +371,18 @@ split_attention_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, c
     __syncthreads();
     const int* table = block_table + int64_t(sg) * max_blocks;
     const int key = base + tid;
-    const bool valid = key >= lo && key <= pos;
+    const bool valid = key <= pos && (key >= lo || key < keep_end);
+    // a key in the gap between the kept keys and the window takes the row of the chunk's first visible key (weight 0)
+    const int first_seen = base < keep_end ? base : max(lo, base);
+    const bool in_gap = !valid && key > first_seen && key < lo;
     float acc[GB];
 #pragma unroll
     for (int gq = 0; gq < GB; gq++) acc[gq] = 0.0f;
     bool have = false;
-    if (valid) {
+    if (in_gap) {
+        const int page = table[first_seen / page_size];
+        rowoff[tid] = (page < 0 || page >= n_pages) ? 0 : (int64_t(page) * n_kv + g) * page_size + first_seen % page_size;
+    } else if (valid) {
         const int page = table[key / page_size];
         if (page < 0 || page >= n_pages) {
             if (status) atomicExch(status, 3);
@@ -419,6 +437,7 @@ split_attention_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, c
             if (have) {
                 sv = acc[gq] * scale;
                 if (dist_bias) sv += dist_bias[int64_t(min(pos - key, bias_len - 1)) * n_heads + h0 + gq];
+                if (slopes) sv = fmaf(-slopes[h0 + gq], float(pos - key), sv);
             }
             sc[gq * KC + tid] = sv;
         }
@@ -439,7 +458,7 @@ split_attention_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, c
         if (lane == 0) { ml[2 * gq] = m; ml[2 * gq + 1] = l; }
     }
     __syncthreads();
-    const int j0 = max(lo, base) - base, j1 = min(pos, base + KC - 1) - base;
+    const int j0 = first_seen - base, j1 = (ci < nk ? min(keep_end - 1, base + KC - 1) : min(pos, base + KC - 1)) - base;
     if (vec_v) {
         // Value rows reach shared memory VT keys at a time, by 16-byte loads that all threads issue together; then a
         // thread per channel adds them in ascending key order (the same order as the loop below).
@@ -518,7 +537,7 @@ template <typename T>
 __global__ void split_attention_merge_kernel(const float* __restrict__ parts, const int* __restrict__ token_seg,
                                              const int* __restrict__ positions, const int* __restrict__ single_only,
                                              const float* __restrict__ sink, T* __restrict__ out, int64_t n_rows, int n_heads,
-                                             int dv, int window, int n_chunks) {
+                                             int dv, int window, int n_chunks, int keep_first) {
     ib::pdl_wait();
     const int lane = threadIdx.x & 31;
     const int64_t r = int64_t(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -529,7 +548,8 @@ __global__ void split_attention_merge_kernel(const float* __restrict__ parts, co
     if (single_only && single_only[sg + 1] - single_only[sg] > 1) return;
     const int pos = positions[t];
     const int lo = window > 0 ? max(0, pos - window + 1) : 0;
-    const int n = min(n_chunks, pos / KC - lo / KC + 1);
+    const int nk = min((min(keep_first, lo) + KC - 1) / KC, lo / KC);
+    const int n = min(n_chunks, nk + pos / KC - lo / KC + 1);
     const float* mine = parts + r * n_chunks * int64_t(dv + 2);
     float m = sink ? sink[h] : -INFINITY;
     for (int i = 0; i < n; i++) m = fmaxf(m, mine[i * int64_t(dv + 2)]);
@@ -690,8 +710,12 @@ __global__ void tail_update_kernel(const float* __restrict__ rows, int64_t ld, i
 // every segment in order:
 //   MODE 0 (a decay per key channel):  S <- diag(a_t) S + k_t v_t^T;               o_t = S^T q_t
 //   MODE 1 (gated delta rule):         S <- g_t S;  u = beta_t (v_t - S^T k_t);  S <- S + k_t u^T;  o_t = S^T q_t
+//   MODE 2 (a constant decay per head):  S <- g S + k_t v_t^T;                       o_t = S^T q_t
+//   MODE 3 (a decay per key channel, a bonus for the current token):
+//                                       o_t = (S + diag(u) k_t v_t^T)^T q_t;  then  S <- diag(a_t) S + k_t v_t^T
 // MODE 1 is computed from the old state in one sweep: r = S^T k, p = S^T q, u = beta (v - g r), o = g p + u (k.q),
-// S <- g S + k u^T, with k.q given per token (aux rows).
+// S <- g S + k u^T, with k.q given per token (aux rows). MODE 2 reads g at aux_col + h of the token's aux row (a
+// leading dimension of 0: one row for every token). MODE 3 reads its decays as MODE 0 and u [heads, d] from `bonus`.
 // A column of S belongs to LK = 8 neighbouring lanes, lane j of them keeping rows j R .. j R + R - 1 in registers
 // (R >= d / 8, rows beyond d are zero and stay zero); a warp has 4 columns, a CTA `cb` columns of one (segment, head).
 // Column sums are added within a lane in four chains and across the 8 lanes by shuffles, in an order that depends on
@@ -711,7 +735,7 @@ __device__ __forceinline__ void copy_async4(float* smem_dst, const float* gmem_s
 // One token's operands of a thread: its R rows of q, k (and of the decays), the value of its column, the scalars.
 template <int R, int MODE>
 struct ScanOperands {
-    float4 q[R / 4], k[R / 4], a[MODE == 0 ? R / 4 : 1];
+    float4 q[R / 4], k[R / 4], a[(MODE == 0 || MODE == 3) ? R / 4 : 1];
     float v, g, beta, kq;
     __device__ __forceinline__ void load(const float* qs, const float* ks, const float* as, const float* vs, int c, int dpp, int off,
                                          int cb, int col_l) {
@@ -719,7 +743,7 @@ struct ScanOperands {
         const float4* k4 = reinterpret_cast<const float4*>(ks + c * dpp + off);
 #pragma unroll
         for (int i = 0; i < R / 4; i++) { q[i] = q4[i]; k[i] = k4[i]; }
-        if (MODE == 0) {
+        if (MODE == 0 || MODE == 3) {
             const float4* a4 = reinterpret_cast<const float4*>(as + c * dpp + off);
 #pragma unroll
             for (int i = 0; i < R / 4; i++) a[i] = a4[i];
@@ -732,8 +756,50 @@ struct ScanOperands {
 
 // One token through a thread's share of the state; returns the column's read-out (valid in every lane of its group).
 template <int R, int MODE>
-__device__ __forceinline__ float scan_token(float (&S)[R], const ScanOperands<R, MODE>& x) {
+__device__ __forceinline__ float scan_token(float (&S)[R], const ScanOperands<R, MODE>& x, const float* U) {
     const float v = x.v;
+    if (MODE == 2) {
+        const float g = x.g;
+        float p0 = 0.0f, p1 = 0.0f, p2 = 0.0f, p3 = 0.0f;
+#pragma unroll
+        for (int i4 = 0; i4 < R / 4; i4++) {
+            const float4 k = x.k[i4], q = x.q[i4];
+            S[4 * i4 + 0] = fmaf(g, S[4 * i4 + 0], k.x * v);
+            S[4 * i4 + 1] = fmaf(g, S[4 * i4 + 1], k.y * v);
+            S[4 * i4 + 2] = fmaf(g, S[4 * i4 + 2], k.z * v);
+            S[4 * i4 + 3] = fmaf(g, S[4 * i4 + 3], k.w * v);
+            p0 = fmaf(S[4 * i4 + 0], q.x, p0);
+            p1 = fmaf(S[4 * i4 + 1], q.y, p1);
+            p2 = fmaf(S[4 * i4 + 2], q.z, p2);
+            p3 = fmaf(S[4 * i4 + 3], q.w, p3);
+        }
+        float p = (p0 + p1) + (p2 + p3);
+        p += __shfl_xor_sync(0xffffffffu, p, 1);
+        p += __shfl_xor_sync(0xffffffffu, p, 2);
+        p += __shfl_xor_sync(0xffffffffu, p, 4);
+        return p;
+    }
+    if (MODE == 3) {
+        float p0 = 0.0f, p1 = 0.0f, p2 = 0.0f, p3 = 0.0f;
+#pragma unroll
+        for (int i4 = 0; i4 < R / 4; i4++) {
+            const float4 a = x.a[i4], k = x.k[i4], q = x.q[i4];
+            const float w0 = k.x * v, w1 = k.y * v, w2 = k.z * v, w3 = k.w * v;
+            p0 = fmaf(fmaf(U[4 * i4 + 0], w0, S[4 * i4 + 0]), q.x, p0);
+            p1 = fmaf(fmaf(U[4 * i4 + 1], w1, S[4 * i4 + 1]), q.y, p1);
+            p2 = fmaf(fmaf(U[4 * i4 + 2], w2, S[4 * i4 + 2]), q.z, p2);
+            p3 = fmaf(fmaf(U[4 * i4 + 3], w3, S[4 * i4 + 3]), q.w, p3);
+            S[4 * i4 + 0] = fmaf(a.x, S[4 * i4 + 0], w0);
+            S[4 * i4 + 1] = fmaf(a.y, S[4 * i4 + 1], w1);
+            S[4 * i4 + 2] = fmaf(a.z, S[4 * i4 + 2], w2);
+            S[4 * i4 + 3] = fmaf(a.w, S[4 * i4 + 3], w3);
+        }
+        float p = (p0 + p1) + (p2 + p3);
+        p += __shfl_xor_sync(0xffffffffu, p, 1);
+        p += __shfl_xor_sync(0xffffffffu, p, 2);
+        p += __shfl_xor_sync(0xffffffffu, p, 4);
+        return p;
+    }
     if (MODE == 0) {
         float p0 = 0.0f, p1 = 0.0f, p2 = 0.0f, p3 = 0.0f;
 #pragma unroll
@@ -797,11 +863,14 @@ __global__ void __launch_bounds__(256)
 state_scan_kernel(const float* __restrict__ rows, int64_t ld, int q_col, int k_col, int v_col,
                   const float* __restrict__ aux, int64_t lda, int aux_col, float* __restrict__ state,
                   const int* __restrict__ seg_start, const int* __restrict__ seg_slot, float* __restrict__ raw_out,
-                  int n_heads, int heads_per_qk, int d, int dv, int cb, int chunk, int write_state, int pipelined) {
+                  int n_heads, int heads_per_qk, int d, int dv, int cb, int chunk, int write_state, int pipelined,
+                  const float* __restrict__ bonus) {
     extern __shared__ __align__(16) float sm[];
     constexpr int RP = R + 4, DPP = LK * RP;
+    constexpr bool ROWS = MODE == 0 || MODE == 3;      // the decays are rows like q and k
+    constexpr int N_SCAL = MODE == 1 ? 3 : 1;          // scalars per token otherwise
     const int n_buf = pipelined ? 2 : 1;
-    const int a_tok = MODE == 0 ? DPP : 4;
+    const int a_tok = ROWS ? DPP : 4;
     float* qs = sm;                          // [n_buf][chunk][DPP]
     float* ks = qs + n_buf * chunk * DPP;
     float* as = ks + n_buf * chunk * DPP;    // MODE 0: [n_buf][chunk][DPP] decays; MODE 1: [n_buf][chunk][4] g, beta, k.q
@@ -821,6 +890,11 @@ state_scan_kernel(const float* __restrict__ rows, int64_t ld, int q_col, int k_c
     float S[R];
 #pragma unroll
     for (int i = 0; i < R; i++) S[i] = (live && k0 + i < d) ? S_g[int64_t(k0 + i) * dv + col] : 0.0f;
+    float U[MODE == 3 ? R : 1];
+    if (MODE == 3) {
+#pragma unroll
+        for (int i = 0; i < R; i++) U[i] = k0 + i < d ? bonus[int64_t(h) * d + k0 + i] : 0.0f;
+    }
     __syncthreads();
 
     auto request = [&](int c0, int b) {      // asynchronous copies of the chunk that starts at token c0 into buffer b
@@ -832,11 +906,11 @@ state_scan_kernel(const float* __restrict__ rows, int64_t ld, int q_col, int k_c
             const float* row = rows + (t0 + c0 + c) * ld;
             copy_async16(qs + dst, row + q_col + hq * d + j);
             copy_async16(ks + dst, row + k_col + hq * d + j);
-            if (MODE == 0) copy_async16(as + dst, aux + (t0 + c0 + c) * lda + aux_col + h * d + j);
+            if (ROWS) copy_async16(as + dst, aux + (t0 + c0 + c) * lda + aux_col + h * d + j);
         }
-        if (MODE == 1) {
-            for (int idx = tid; idx < n * 3; idx += blockDim.x) {
-                const int c = idx / 3, e = idx - c * 3;
+        if (!ROWS) {
+            for (int idx = tid; idx < n * N_SCAL; idx += blockDim.x) {
+                const int c = idx / N_SCAL, e = idx - c * N_SCAL;
                 const float* ar = aux + (t0 + c0 + c) * lda + aux_col;
                 copy_async4(as + (b * chunk + c) * 4 + e, ar + (e == 0 ? h : (e == 1 ? n_heads + h : 2 * n_heads + hq)));
             }
@@ -855,14 +929,16 @@ state_scan_kernel(const float* __restrict__ rows, int64_t ld, int q_col, int k_c
             const float* row = rows + (t0 + c0 + c) * ld;
             qs[dst] = row[q_col + hq * d + j];
             ks[dst] = row[k_col + hq * d + j];
-            if (MODE == 0) as[dst] = aux[(t0 + c0 + c) * lda + aux_col + h * d + j];
+            if (ROWS) as[dst] = aux[(t0 + c0 + c) * lda + aux_col + h * d + j];
         }
-        if (MODE == 1) {
+        if (!ROWS) {
             for (int c = tid; c < n; c += blockDim.x) {
                 const float* ar = aux + (t0 + c0 + c) * lda + aux_col;
                 as[c * 4 + 0] = ar[h];
-                as[c * 4 + 1] = ar[n_heads + h];
-                as[c * 4 + 2] = ar[2 * n_heads + hq];
+                if (MODE == 1) {
+                    as[c * 4 + 1] = ar[n_heads + h];
+                    as[c * 4 + 2] = ar[2 * n_heads + hq];
+                }
             }
         }
         for (int idx = tid; idx < n * cb; idx += blockDim.x) {
@@ -894,7 +970,7 @@ state_scan_kernel(const float* __restrict__ rows, int64_t ld, int q_col, int k_c
         cur.load(qb, kb, ab, vb, 0, DPP, off, cb, col_l);
         for (int c = 0; c < n; c++) {
             if (c + 1 < n) nxt.load(qb, kb, ab, vb, c + 1, DPP, off, cb, col_l);
-            const float o = scan_token<R, MODE>(S, cur);
+            const float o = scan_token<R, MODE>(S, cur, U);
             if (lk == 0 && live) raw_out[((t0 + c0 + c) * n_heads + h) * int64_t(dv) + col] = o;
             cur = nxt;
         }
@@ -978,7 +1054,7 @@ IB_EXPORT int ib_glu_act(const void* rows, int64_t ld, int64_t gate_col, int64_t
                          int64_t n_tokens, int dtype, cudaStream_t stream) {
     const int64_t n = n_tokens * width;
     if (n <= 0) return IB_OK;
-    if (kind != 0 && kind != 1) return ib::fail(IB_ERR_ARG, "ib_glu_act: unknown activation %d", kind);
+    if (kind < 0 || kind > 2) return ib::fail(IB_ERR_ARG, "ib_glu_act: unknown activation %d", kind);
     if (dtype == IB_F32)
         IB_LAUNCH(glu_act_kernel<float>, blocks_for(n, 256), 256, 0, (const float*)rows, ld, gate_col, up_col, width, kind, limit,
                   limit2, slope, scale, group, n_groups, (float*)out, n);
@@ -1025,8 +1101,8 @@ IB_EXPORT int ib_rownorm_store(const void* rows, int64_t ld, int col0, const flo
 }
 
 // Floats of workspace that ib_attention_split needs for n_tokens tokens whose queries see up to `visible` keys.
-IB_EXPORT int64_t ib_attention_split_workspace(int64_t n_tokens, int n_heads, int dv, int visible) {
-    const int64_t n_chunks = (visible + KC - 1) / KC + 1;
+IB_EXPORT int64_t ib_attention_split_workspace(int64_t n_tokens, int n_heads, int dv, int visible, int keep_first) {
+    const int64_t n_chunks = (visible + KC - 1) / KC + 1 + (keep_first > 0 ? (keep_first + KC - 1) / KC : 0);
     return n_tokens * n_heads * n_chunks * (dv + 2);
 }
 
@@ -1036,14 +1112,15 @@ IB_EXPORT int ib_attention_split(const void* q, const void* k_cache, const void*
                                  const int* token_seg, const int* positions, const int* single_only, void* out, float* workspace,
                                  int64_t n_tokens, int n_heads, int n_kv, int d, int dv, int page_size, int window, float scale,
                                  int64_t n_pages, const float* dist_bias, int bias_len, const float* sink, int visible, int dtype,
-                                 int* status, cudaStream_t stream) {
+                                 int* status, cudaStream_t stream, int keep_first, const float* slopes) {
     if (n_tokens <= 0) return IB_OK;
     if (n_kv <= 0 || n_heads % n_kv || n_heads / n_kv > GMAX)
         return ib::fail(IB_ERR_ARG, "ib_attention_split: %d heads on %d kv heads (groups of up to %d)", n_heads, n_kv, GMAX);
     if (d <= 0 || dv <= 0 || d > 512 || dv > 1024 || page_size <= 0 || visible <= 0 || !workspace)
         return ib::fail(IB_ERR_ARG, "ib_attention_split: bad sizes");
     if (dist_bias && bias_len <= 0) return ib::fail(IB_ERR_ARG, "ib_attention_split: a distance bias needs at least one row");
-    const int n_chunks = (visible + KC - 1) / KC + 1;
+    if (keep_first < 0 || (keep_first > 0 && window <= 0)) keep_first = 0;     // without a window every key is seen anyway
+    const int n_chunks = (visible + KC - 1) / KC + 1 + (keep_first > 0 ? (keep_first + KC - 1) / KC : 0);
     if (n_kv > 65535 || n_chunks > 65535) return ib::fail(IB_ERR_ARG, "ib_attention_split: too many kv heads or chunks");
     const int group = n_heads / n_kv;
     const size_t item = dtype == IB_F32 ? 4 : 2;
@@ -1059,7 +1136,7 @@ IB_EXPORT int ib_attention_split(const void* q, const void* k_cache, const void*
 #define IB_SPLIT(TT, GG)                                                                                                          \
     IB_LAUNCH((split_attention_kernel<TT, GG>), grid, KC, smem, (const TT*)q, (const TT*)k_cache, (const TT*)v_cache, block_table, \
               max_blocks, token_seg, positions, single_only, workspace, n_heads, n_kv, d, dv, page_size, window, scale, n_pages,  \
-              dist_bias, bias_len, n_chunks, vec, vec_v, status)
+              dist_bias, bias_len, n_chunks, vec, vec_v, status, keep_first, slopes)
 #define IB_SPLIT_BY_GROUP(TT)                                                                                                     \
     do {                                                                                                                          \
         if (gb == 1) IB_SPLIT(TT, 1); else if (gb == 2) IB_SPLIT(TT, 2); else if (gb == 4) IB_SPLIT(TT, 4);                       \
@@ -1068,11 +1145,11 @@ IB_EXPORT int ib_attention_split(const void* q, const void* k_cache, const void*
     if (dtype == IB_F32) {
         IB_SPLIT_BY_GROUP(float);
         IB_LAUNCH(split_attention_merge_kernel<float>, blocks_for(rows, 4), 128, 0, workspace, token_seg, positions, single_only, sink,
-                  (float*)out, rows, n_heads, dv, window, n_chunks);
+                  (float*)out, rows, n_heads, dv, window, n_chunks, keep_first);
     } else if (dtype == IB_BF16) {
         IB_SPLIT_BY_GROUP(bf16);
         IB_LAUNCH(split_attention_merge_kernel<bf16>, blocks_for(rows, 4), 128, 0, workspace, token_seg, positions, single_only, sink,
-                  (bf16*)out, rows, n_heads, dv, window, n_chunks);
+                  (bf16*)out, rows, n_heads, dv, window, n_chunks, keep_first);
     } else {
         return ib::fail(IB_ERR_ARG, "ib_attention_split: unknown dtype %d", dtype);
     }
@@ -1126,22 +1203,26 @@ template <int R, int MODE>
 static int launch_scan(dim3 grid, int threads, size_t smem, cudaStream_t stream, const float* rows, int64_t ld, int q_col,
                        int k_col, int v_col, const float* aux, int64_t lda, int aux_col, float* state, const int* seg_start,
                        const int* seg_slot, float* raw_out, int n_heads, int hpq, int d, int dv, int cb, int chunk, int write_state,
-                       int pipelined) {
+                       int pipelined, const float* bonus) {
     IB_LAUNCH((state_scan_kernel<R, MODE>), grid, threads, smem, rows, ld, q_col, k_col, v_col, aux, lda, aux_col, state, seg_start,
-              seg_slot, raw_out, n_heads, hpq, d, dv, cb, chunk, write_state, pipelined);
+              seg_slot, raw_out, n_heads, hpq, d, dv, cb, chunk, write_state, pipelined, bonus);
     return ib::check_launch("ib_state_scan");
 }
 
-// mode 0: a decay per key channel (aux: decays at aux_col + h d); mode 1: gated delta rule (aux: g, beta, k.q).
+// mode 0: a decay per key channel (aux: decays at aux_col + h d); mode 1: gated delta rule (aux: g, beta, k.q);
+// mode 2: a decay per head (aux: at aux_col + h; lda 0: the same for every token); mode 3: as mode 0 with the read-out
+// before the write and `bonus` [heads, d] on the current token.
 // `spread` (prompt portions): a head's columns go to more, smaller CTAs until there is about one per SM (sm_count).
 IB_EXPORT int ib_state_scan(int mode, const float* rows, int64_t ld, int q_col, int k_col, int v_col, const float* aux,
                             int64_t lda, int aux_col, float* state, const int* seg_start, const int* seg_slot,
                             float* raw_out, int n_segments, int n_heads, int heads_per_qk, int d, int dv, int write_state,
-                            int spread, int sm_count, cudaStream_t stream) {
+                            int spread, int sm_count, cudaStream_t stream, const float* bonus) {
     if (n_segments <= 0) return IB_OK;
     if (n_heads <= 0 || n_heads > 65535 || heads_per_qk <= 0 || n_heads % heads_per_qk || d <= 0 || dv <= 0 || d > LK * 32)
         return ib::fail(IB_ERR_ARG, "ib_state_scan: %d heads with a state of %d x %d do not fit", n_heads, d, dv);
-    if (mode != 0 && mode != 1) return ib::fail(IB_ERR_ARG, "ib_state_scan: unknown mode %d", mode);
+    if (mode < 0 || mode > 3) return ib::fail(IB_ERR_ARG, "ib_state_scan: unknown mode %d", mode);
+    if (mode == 3 && !bonus) return ib::fail(IB_ERR_ARG, "ib_state_scan: mode 3 needs the bonus");
+    const bool decay_rows = mode == 0 || mode == 3;
     const int r = d <= 32 ? 4 : (d <= 64 ? 8 : (d <= 128 ? 16 : 32));
     int cb = 32;
     while (cb > 4 && cb / 2 >= dv) cb /= 2;                     // no CTA wider than the head
@@ -1152,10 +1233,10 @@ IB_EXPORT int ib_state_scan(int mode, const float* rows, int64_t ld, int q_col, 
     // asynchronous copies of rows as they lie need every offset and size on 16 bytes; prompt portions only (a step of
     // single tokens has nothing to copy ahead)
     const int pipelined = spread && d % 4 == 0 && dv % 4 == 0 && cb % 4 == 0 && ld % 4 == 0 && q_col % 4 == 0 && k_col % 4 == 0 &&
-                          v_col % 4 == 0 && (mode != 0 || (lda % 4 == 0 && aux_col % 4 == 0 && !(uintptr_t(aux) & 15))) &&
+                          v_col % 4 == 0 && (!decay_rows || (lda % 4 == 0 && aux_col % 4 == 0 && !(uintptr_t(aux) & 15))) &&
                           !(uintptr_t(rows) & 15);
     const int dpp = LK * (r + 4), n_buf = pipelined ? 2 : 1;
-    const int per_token = 2 * dpp + (mode == 0 ? dpp : 4) + cb;
+    const int per_token = 2 * dpp + (decay_rows ? dpp : 4) + cb;
     int chunk = 11264 / (n_buf * per_token);
     chunk = chunk < 1 ? 1 : (chunk > 16 ? 16 : chunk);
     const size_t smem = size_t(n_buf) * chunk * per_token * sizeof(float);
@@ -1164,7 +1245,19 @@ IB_EXPORT int ib_state_scan(int mode, const float* rows, int64_t ld, int q_col, 
     const int threads = cb * LK;
 #define IB_SCAN(RR, MM)                                                                                                          \
     return launch_scan<RR, MM>(grid, threads, smem, stream, rows, ld, q_col, k_col, v_col, aux, lda, aux_col, state, seg_start, \
-                               seg_slot, raw_out, n_heads, heads_per_qk, d, dv, cb, chunk, write_state, pipelined)
+                               seg_slot, raw_out, n_heads, heads_per_qk, d, dv, cb, chunk, write_state, pipelined, bonus)
+    if (mode == 2) {
+        if (r == 4) IB_SCAN(4, 2);
+        if (r == 8) IB_SCAN(8, 2);
+        if (r == 16) IB_SCAN(16, 2);
+        IB_SCAN(32, 2);
+    }
+    if (mode == 3) {
+        if (r == 4) IB_SCAN(4, 3);
+        if (r == 8) IB_SCAN(8, 3);
+        if (r == 16) IB_SCAN(16, 3);
+        IB_SCAN(32, 3);
+    }
     if (mode == 0) {
         if (r == 4) IB_SCAN(4, 0);
         if (r == 8) IB_SCAN(8, 0);

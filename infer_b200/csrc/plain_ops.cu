@@ -316,6 +316,8 @@ rope_kv_write_vec_kernel(const bf16* __restrict__ qkv, const float* __restrict__
 // [kv_heads, page_size, v_dim] then), and the output rows are [heads, v_dim].
 // Optional: a learned bias per (distance, head), dist_bias[min(p - j, bias_len - 1) * heads + h], added to the scaled
 // score; and a sink per head, a logit without key or value that only enters the softmax denominator, once.
+// keep_first > 0: a windowed query also reads the keys below keep_first (tiles that hold neither those nor keys of the
+// window are skipped). slopes [heads]: slopes[h] * (p - j) is taken off the scaled score.
 constexpr int AT = 128;
 
 template <typename T>
@@ -325,7 +327,7 @@ attention_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, const T
                  const int* __restrict__ positions, T* __restrict__ out, int n_heads, int n_kv, int head_dim, int v_dim,
                  int page_size, int window, float scale, int64_t n_pages, int* status,
                  const float* __restrict__ dist_bias, int bias_len, const float* __restrict__ sink,
-                 const int* __restrict__ single_only) {
+                 const int* __restrict__ single_only, int keep_first, const float* __restrict__ slopes) {
     ib::pdl_wait();
     // single_only (a step's seg_start): tokens of segments with two or more tokens are another kernel's
     if (single_only) {
@@ -344,6 +346,8 @@ attention_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, const T
     const int tid = threadIdx.x;
     const int pos = positions[t];
     const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+    const int keep_end = min(keep_first, lo);          // keys below it are read although the window has passed them
+    const float slope = slopes ? slopes[h] : 0.0f;
     const int* table = block_table + int64_t(token_seg[t]) * max_blocks;
 
     for (int d = tid; d < head_dim; d += AT) qs[d] = ib::to_f32(q[(t * n_heads + h) * head_dim + d]);
@@ -354,9 +358,13 @@ attention_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, const T
     }
     __syncthreads();
 
-    for (int tile = (lo / AT) * AT; tile <= pos; tile += AT) {
+    for (int tile = keep_end > 0 ? 0 : (lo / AT) * AT; tile <= pos; tile += AT) {
+        if (tile >= keep_end && tile + AT <= lo) {     // nothing of this tile is seen: on to the window's first tile
+            tile = (lo / AT) * AT - AT;
+            continue;
+        }
         const int j = tile + tid;
-        const bool valid = j >= lo && j <= pos;
+        const bool valid = j <= pos && (j >= lo || j < keep_end);
         float s = -INFINITY;
         if (valid) {
             const int page = table[j / page_size];
@@ -371,6 +379,7 @@ attention_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, const T
                 for (int d = 0; d < head_dim; d++) dot = fmaf(qs[d], ib::to_f32(kr[d]), dot);
                 s = dot * scale;
                 if (dist_bias) s += dist_bias[int64_t(min(pos - j, bias_len - 1)) * n_heads + h];
+                if (slopes) s = fmaf(-slope, float(pos - j), s);
             }
         }
         const float tile_max = ib::block_max(s, red);
@@ -382,8 +391,9 @@ attention_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, const T
         l = l * corr + tile_sum;
         acc0 *= corr;
         acc1 *= corr;
-        const int jj0 = max(lo, tile) - tile, jj1 = min(pos, tile + AT - 1) - tile;
+        const int jj0 = (tile < keep_end ? tile : max(lo, tile)) - tile, jj1 = min(pos, tile + AT - 1) - tile;
         for (int jj = jj0; jj <= jj1; jj++) {
+            if (tile + jj >= keep_end && tile + jj < lo) continue;       // between the kept keys and the window
             const float pj = ps[jj];
             const T* vr = v_cache + rowoff[jj] * v_dim;
             if (tid < v_dim) acc0 = fmaf(pj, ib::to_f32(vr[tid]), acc0);
@@ -706,7 +716,8 @@ IB_EXPORT int ib_attention_plain(const void* q, const void* k_cache, const void*
                                  int64_t max_blocks, const int* token_seg, const int* positions, void* out,
                                  int64_t n_tokens, int n_heads, int n_kv, int head_dim, int page_size, int window,
                                  float scale, int64_t n_pages, int dtype, int* status, cudaStream_t stream, int v_dim,
-                                 const float* dist_bias, int bias_len, const float* sink, const int* single_only) {
+                                 const float* dist_bias, int bias_len, const float* sink, const int* single_only, int keep_first,
+                                 const float* slopes) {
     if (n_tokens <= 0) return IB_OK;
     if (dist_bias && bias_len <= 0) return ib::fail(IB_ERR_ARG, "ib_attention_plain: a distance bias needs at least one row");
     if (v_dim <= 0) v_dim = head_dim;                       // values as long as keys
@@ -719,11 +730,11 @@ IB_EXPORT int ib_attention_plain(const void* q, const void* k_cache, const void*
     if (dtype == IB_F32)
         IB_LAUNCH(attention_kernel<float>, grid, AT, smem, (const float*)q, (const float*)k_cache, (const float*)v_cache,
             block_table, max_blocks, token_seg, positions, (float*)out, n_heads, n_kv, head_dim, v_dim, page_size, window, scale, n_pages, status,
-            dist_bias, bias_len, sink, single_only);
+            dist_bias, bias_len, sink, single_only, window > 0 && keep_first > 0 ? keep_first : 0, slopes);
     else if (dtype == IB_BF16)
         IB_LAUNCH(attention_kernel<bf16>, grid, AT, smem, (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache,
             block_table, max_blocks, token_seg, positions, (bf16*)out, n_heads, n_kv, head_dim, v_dim, page_size, window, scale, n_pages, status,
-            dist_bias, bias_len, sink, single_only);
+            dist_bias, bias_len, sink, single_only, window > 0 && keep_first > 0 ? keep_first : 0, slopes);
     else
         return ib::fail(IB_ERR_ARG, "ib_attention_plain: unknown dtype %d", dtype);
     return ib::check_launch("ib_attention_plain");

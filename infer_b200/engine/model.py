@@ -37,7 +37,7 @@ class Model:
 
     def _build_block(self, ls: LayerSpec, weights) -> Block:
         parts = {slot: self._build_part(family, pspec, weights) for slot, (family, pspec) in ls.parts.items()}
-        return part_class("block", ls.block)(**parts)
+        return part_class("block", ls.block)(**parts, **dict(ls.options))
 
     def all_parts(self):
         yield self.embedding

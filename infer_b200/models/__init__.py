@@ -6,7 +6,7 @@ command lines and the benchmark build random models from.
 import json
 import os
 
-from . import qwen2, ruvenex, fozerax, pefazen  # noqa: F401
+from . import qwen2, ruvenex, fozerax, pefazen, biravik  # noqa: F401
 
 PRESET_DIR = os.path.join(os.path.dirname(os.path.abspath(__file__)), "presets")
 

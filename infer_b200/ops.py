@@ -190,13 +190,15 @@ def attention_plain(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
                     window: Optional[int], scale: float, status: Optional[torch.Tensor] = None,
                     v_head_dim: Optional[int] = None, dist_bias: Optional[torch.Tensor] = None,
                     sink: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
-                    single_only: Optional[torch.Tensor] = None) -> torch.Tensor:
+                    single_only: Optional[torch.Tensor] = None, keep_first: int = 0,
+                    slopes: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Causal attention of every token over its request's pages; returns [T, heads*v_head_dim] (values are as long
     as keys unless ``v_head_dim`` says otherwise; the value pages are [pages, kv_heads, page_size, v_head_dim]).
     ``dist_bias`` float32 [L, heads]: row min(distance, L - 1) is added to the scaled scores of a query's keys;
     ``sink`` float32 [heads]: a logit per head that enters the softmax denominator only. ``out``: write there;
     ``single_only`` (the step's seg_start): only tokens that are a segment of their own are computed, the other rows
-    of ``out`` stay as they are."""
+    of ``out`` stay as they are. ``keep_first``: a windowed query also sees the keys at positions below it.
+    ``slopes`` float32 [heads]: slopes[h] * (query position - key position) is taken off the scaled score."""
     _check(q, "q")
     T = q.shape[0]
     vd = int(v_head_dim or head_dim)
@@ -219,12 +221,15 @@ def attention_plain(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
             raise KernelError(f"dist_bias must be [distances, {n_heads}], got {tuple(dist_bias.shape)}")
     if sink is not None:
         _check(sink, "sink", torch.float32, (n_heads,))
+    if slopes is not None:
+        _check(slopes, "slopes", torch.float32, (n_heads,))
     f = _fn("plain", "ib_attention_plain", [c_void_p] * 4 + [c_int64] + [c_void_p] * 3 + [c_int64] + [c_int] * 5 +
-            [c_float, c_int64, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p])
+            [c_float, c_int64, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p])
     _call(f, q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), block_table.data_ptr(), block_table.shape[1],
           token_seg.data_ptr(), positions.data_ptr(), out.data_ptr(), T, n_heads, n_kv, head_dim, page_size,
           int(window or 0), float(scale), n_pages, dtype_code(q.dtype), _ptr(status), _stream(), vd,
-          _ptr(dist_bias), 0 if dist_bias is None else dist_bias.shape[0], _ptr(sink), _ptr(single_only))
+          _ptr(dist_bias), 0 if dist_bias is None else dist_bias.shape[0], _ptr(sink), _ptr(single_only), int(keep_first or 0),
+          _ptr(slopes))
     return out
 
 
@@ -521,7 +526,7 @@ def dual_norm_sum(a: torch.Tensor, wa: torch.Tensor, sa: float, b: torch.Tensor,
     return out, copy
 
 
-GLU_KINDS = {"gelu_tanh": 0, "clipped_swish": 1}
+GLU_KINDS = {"gelu_tanh": 0, "clipped_swish": 1, "swish": 2}
 
 
 def glu_act(rows: torch.Tensor, gate_col: int, up_col: int, width: int, kind: str, limit: float = 0.0,
@@ -529,7 +534,7 @@ def glu_act(rows: torch.Tensor, gate_col: int, up_col: int, width: int, kind: st
             n_groups: int = 0) -> torch.Tensor:
     """The hidden layer of a gated feed-forward, from rows [T, ld] that hold gate and up columns -> [T, width].
     "gelu_tanh": gelu_tanh(g) * u. "clipped_swish": g' = min(g, limit), u' = clamp(u, -limit, limit),
-    g' * sigmoid(slope * g') * (u' + 1). With ``scale`` float32 [T, n_groups]: block e of ``group`` columns is
+    g' * sigmoid(slope * g') * (u' + 1). "swish": g * sigmoid(g) * u. With ``scale`` float32 [T, n_groups]: block e of ``group`` columns is
     multiplied by scale[t, e]; columns from n_groups * group on are not scaled and use ``limit2``."""
     _check(rows, "rows")
     T, ld = rows.shape
@@ -588,11 +593,12 @@ def rownorm_store(rows: torch.Tensor, col0: int, wq: Optional[torch.Tensor], wk:
 
 
 def attention_split(q, k_cache, v_cache, block_table, step, n_heads, n_kv, head_dim, v_head_dim, window, scale,
-                    dist_bias=None, sink=None, out=None, single_only=False):
+                    dist_bias=None, sink=None, out=None, single_only=False, keep_first=0, slopes=None):
     """Paged attention with keys split over CTAs (chunks of 128 keys aligned to absolute positions, merged in
     ascending order), for tokens that read a few hundred keys each: decoded tokens of a windowed layer. Takes a
     distance bias float32 [L, heads] and a sink float32 [heads]. With ``single_only`` only tokens that are a segment
-    of their own are computed (into ``out``, whose other rows stay)."""
+    of their own are computed (into ``out``, whose other rows stay). ``keep_first``: a windowed query also sees the keys
+    at positions below it; ``slopes`` float32 [heads]: slopes[h] * distance is taken off the scaled score."""
     _check(q, "q")
     T = q.shape[0]
     n_pages, ckv, page_size, chd = k_cache.shape
@@ -611,15 +617,18 @@ def attention_split(q, k_cache, v_cache, block_table, step, n_heads, n_kv, head_
         _check(out, "out", q.dtype, (T, n_heads * v_head_dim))
     visible = min(int(window), int(step.max_ctx_len)) if window else int(step.max_ctx_len)
     visible = max(visible, 1)
-    n_ws = int(_fn("mix", "ib_attention_split_workspace", [c_int64, c_int, c_int, c_int], restype=c_int64)(T, n_heads, v_head_dim, visible))
+    keep_first = int(keep_first or 0) if window else 0
+    if slopes is not None:
+        _check(slopes, "slopes", torch.float32, (n_heads,))
+    n_ws = int(_fn("mix", "ib_attention_split_workspace", [c_int64, c_int, c_int, c_int, c_int], restype=c_int64)(T, n_heads, v_head_dim, visible, keep_first))
     ws = torch.empty(n_ws, dtype=torch.float32, device=q.device)
     f = _fn("mix", "ib_attention_split", [c_void_p] * 4 + [c_int64] + [c_void_p] * 5 + [c_int64] + [c_int] * 6 + [c_float, c_int64,
-                                          c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p])
+                                          c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p])
     _call(f, q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), block_table.data_ptr(), block_table.shape[1],
           step.token_seg.data_ptr(), step.positions.data_ptr(), step.seg_start.data_ptr() if single_only else None, out.data_ptr(),
           ws.data_ptr(), T, n_heads, n_kv, head_dim, v_head_dim, page_size, int(window or 0), float(scale), n_pages,
           _ptr(dist_bias), 0 if dist_bias is None else dist_bias.shape[0], _ptr(sink), visible, dtype_code(q.dtype),
-          _ptr(step.status), _stream())
+          _ptr(step.status), _stream(), keep_first, _ptr(slopes))
     return out
 
 
@@ -627,18 +636,22 @@ ATTENTION_SPLIT_GROUP_MAX = 16
 
 
 def attention_window(q, k_cache, v_cache, block_table, step, n_heads, n_kv, head_dim, v_head_dim, window, scale,
-                     dist_bias, sink, dist_bias_by_head=None):
+                     dist_bias, sink, dist_bias_by_head=None, keep_first=0, slopes=None):
     """Attention with a distance bias and a sink on the faster kernels, where they take the shape: prompt portions on
     the tensor-core kernel (bfloat16, keys and values of one size that the kernel is built for), one-token segments
     on the kernel that splits a token's keys over CTAs, into the same rows. None where a shape is refused (the caller
     then uses the plain kernel for everything). ``dist_bias_by_head``: float32 [heads, L], the bias divided by the
-    scale."""
+    scale. ``keep_first`` and ``slopes`` as in attention_split; the tensor-core kernel keeps no first keys (prompt
+    portions of such a layer go to the caller's plain kernel, its single tokens stay here) and takes slopes as the table
+    ``dist_bias_by_head`` (row h: -slope_h * distance / scale)."""
     from . import fast_ops
     if n_heads // n_kv > ATTENTION_SPLIT_GROUP_MAX:
         return None
+    keep_first = int(keep_first or 0) if window else 0
     if step.max_q_len <= 1:
-        return attention_split(q, k_cache, v_cache, block_table, step, n_heads, n_kv, head_dim, v_head_dim, window, scale, dist_bias, sink)
-    if v_head_dim != head_dim or (dist_bias is not None and dist_bias_by_head is None):
+        return attention_split(q, k_cache, v_cache, block_table, step, n_heads, n_kv, head_dim, v_head_dim, window, scale, dist_bias, sink,
+                               keep_first=keep_first, slopes=slopes)
+    if v_head_dim != head_dim or keep_first or ((dist_bias is not None or slopes is not None) and dist_bias_by_head is None):
         return None
     out = fast_ops.attention_prefill_biased(q, k_cache, v_cache, block_table, step, n_heads, n_kv, head_dim, window, scale,
                                             dist_bias_by_head, sink)
@@ -646,7 +659,7 @@ def attention_window(q, k_cache, v_cache, block_table, step, n_heads, n_kv, head
         return None
     if any(n == 1 for n in step.seg_lens):
         attention_split(q, k_cache, v_cache, block_table, step, n_heads, n_kv, head_dim, v_head_dim, window, scale, dist_bias, sink,
-                        out, single_only=True)
+                        out, single_only=True, slopes=slopes)
     return out
 
 
@@ -725,40 +738,66 @@ def tail_update(rows: torch.Tensor, col0: int, tails: torch.Tensor, seg_start: t
           seg_slot.numel(), _stream())
 
 
-SCAN_ROW_DECAY, SCAN_DELTA_RULE = 0, 1
+SCAN_ROW_DECAY, SCAN_DELTA_RULE, SCAN_HEAD_DECAY, SCAN_BONUS = 0, 1, 2, 3
 SCAN_SPREAD_FROM = 8          # segments of more tokens than this spread a head's columns over more CTAs
 
 
 def state_scan(mode: int, rows: torch.Tensor, q_col: int, k_col: int, v_col: int, aux: torch.Tensor, aux_col: int,
                state: torch.Tensor, seg_start: torch.Tensor, seg_slot: torch.Tensor, n_heads: int, heads_per_qk: int,
-               dim: int, v_dim: int, write_state: bool = True, max_len: int = 1) -> torch.Tensor:
+               dim: int, v_dim: int, write_state: bool = True, max_len: int = 1, bonus: Optional[torch.Tensor] = None) -> torch.Tensor:
     """A linear recurrence with a float32 matrix state [slots, heads, dim, v_dim], over the tokens of every segment
     in order. SCAN_ROW_DECAY: S <- diag(a) S + k v^T, o = S^T q, with a in ``aux`` columns aux_col + h * dim.
     SCAN_DELTA_RULE: S <- g S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q, with ``aux`` columns [g (heads) | beta
     (heads) | k.q (heads / heads_per_qk)] from aux_col. q, k at q_col, k_col + (h // heads_per_qk) * dim and v at
-    v_col + h * v_dim of the float32 ``rows``. Returns o float32 [T, heads * v_dim]."""
+    v_col + h * v_dim of the float32 ``rows``. SCAN_HEAD_DECAY: S <- g_h S + k v^T, o = S^T q, with ``aux`` float32
+    [heads] (a constant per head) or [T, ...] with g at column aux_col + h. SCAN_BONUS: o = (S + diag(u) k v^T)^T q, then
+    S <- diag(a) S + k v^T, with a as for SCAN_ROW_DECAY and u = ``bonus`` float32 [heads, dim].
+    Returns o float32 [T, heads * v_dim]."""
     _check(rows, "rows", torch.float32)
     _check(aux, "aux", torch.float32)
     _check(state, "state", torch.float32)
-    T, ld = rows.shape
+    T, ld = rows.shape[-2:]
+    if rows.dim() == 3:
+        # q, k and v lie in planes [n, T, ld] (the results of separate products); a column is then (plane, column)
+        cols = []
+        for c, width in ((q_col, (n_heads // heads_per_qk) * dim), (k_col, (n_heads // heads_per_qk) * dim), (v_col, n_heads * v_dim)):
+            if not (0 <= c[0] < rows.shape[0] and 0 <= c[1] and c[1] + width <= ld):
+                raise KernelError("the q, k or v columns lie outside their plane")
+            cols.append(c[0] * T * ld + c[1])
+        if max(cols) + ld >= 2 ** 31:
+            raise KernelError("the planes are too large for 32-bit columns")
+        q_col, k_col, v_col = cols
+        planes = True
+    else:
+        planes = False
     if tuple(state.shape[1:]) != (n_heads, dim, v_dim):
         raise KernelError(f"state must be [slots, {n_heads}, {dim}, {v_dim}], got {tuple(state.shape)}")
     n_qk = n_heads // heads_per_qk
-    if max(q_col, k_col) + n_qk * dim > ld or v_col + n_heads * v_dim > ld:
+    if not planes and (max(q_col, k_col) + n_qk * dim > ld or v_col + n_heads * v_dim > ld):
         raise KernelError("the q, k or v columns lie outside the rows")
-    need = n_heads * dim if mode == SCAN_ROW_DECAY else 2 * n_heads + n_qk
-    if aux.shape[0] != T or aux_col + need > aux.shape[1]:
-        raise KernelError("the decay columns lie outside their rows")
+    lda = 0
+    if mode == SCAN_HEAD_DECAY and aux.dim() == 1:
+        if aux_col + n_heads > aux.shape[0]:
+            raise KernelError("a decay per head needs one value per head")
+    else:
+        need = {SCAN_ROW_DECAY: n_heads * dim, SCAN_BONUS: n_heads * dim, SCAN_DELTA_RULE: 2 * n_heads + n_qk, SCAN_HEAD_DECAY: n_heads}[mode]
+        if aux.dim() != 2 or aux.shape[0] != T or aux_col + need > aux.shape[1]:
+            raise KernelError("the decay columns lie outside their rows")
+        lda = aux.shape[1]
+    if mode == SCAN_BONUS:
+        if bonus is None:
+            raise KernelError("SCAN_BONUS needs the bonus [heads, dim]")
+        _check(bonus, "bonus", torch.float32, (n_heads, dim))
     S = seg_slot.numel()
     _check(seg_start, "seg_start", torch.int32, (S + 1,))
     out = torch.empty((T, n_heads * v_dim), dtype=torch.float32, device=rows.device)
     spread = int(max_len) >= SCAN_SPREAD_FROM
     sm_count = torch.cuda.get_device_properties(rows.device).multi_processor_count if spread else 0
     f = _fn("mix", "ib_state_scan", [c_int, c_void_p, c_int64, c_int, c_int, c_int, c_void_p, c_int64, c_int, c_void_p, c_void_p,
-                                     c_void_p, c_void_p] + [c_int] * 8 + [c_void_p])
-    _call(f, int(mode), rows.data_ptr(), ld, int(q_col), int(k_col), int(v_col), aux.data_ptr(), aux.shape[1], int(aux_col),
+                                     c_void_p, c_void_p] + [c_int] * 8 + [c_void_p, c_void_p])
+    _call(f, int(mode), rows.data_ptr(), ld, int(q_col), int(k_col), int(v_col), aux.data_ptr(), lda, int(aux_col),
           state.data_ptr(), seg_start.data_ptr(), seg_slot.data_ptr(), out.data_ptr(), S, n_heads, int(heads_per_qk), dim, v_dim,
-          int(write_state), int(spread), sm_count, _stream())
+          int(write_state), int(spread), sm_count, _stream(), _ptr(bonus) if mode == SCAN_BONUS else None)
     return out
 
 
@@ -1057,3 +1096,165 @@ def scale_softcap(logits: torch.Tensor, scale: float, cap: float) -> torch.Tenso
     f = _fn("latent", "ib_scale_softcap", [c_void_p, c_int64, c_float, c_float, c_void_p])
     _call(f, logits.data_ptr(), logits.numel(), float(scale), float(cap), _stream())
     return logits
+
+
+# ----------------------------------------------------------------------------- norms after the sum, per-head query/key norms, shifted mixtures
+
+def sum_norm(x: torch.Tensor, alpha: float, a: torch.Tensor, sa: float, b: Optional[torch.Tensor], sb: float, weight: torch.Tensor,
+             eps: float, copy_dtype: Optional[torch.dtype] = None):
+    """y / sqrt(mean(y^2) + eps) * weight per row with y = alpha x + sa a + sb b (b may be absent), float32 [T, W],
+    written over x. With ``copy_dtype`` also the same rows in that dtype (for a matrix product that reads them);
+    returns (rows, copy or None)."""
+    _check(x, "x", torch.float32)
+    T, W = x.shape
+    _check(a, "a", torch.float32, (T, W))
+    if b is not None:
+        _check(b, "b", torch.float32, (T, W))
+    _check(weight, "weight", torch.float32, (W,))
+    copy = None
+    if copy_dtype is not None and copy_dtype != torch.float32:
+        copy = torch.empty((T, W), dtype=copy_dtype, device=x.device)
+    f = _fn("post", "ib_sum_norm", [c_void_p, c_float, c_void_p, c_float, c_void_p, c_float, c_void_p, c_float, c_void_p, c_void_p,
+                                    c_int, c_int64, c_int64, c_void_p])
+    _call(f, x.data_ptr(), float(alpha), a.data_ptr(), float(sa), _ptr(b), float(sb), weight.data_ptr(), float(eps), x.data_ptr(),
+          _ptr(copy), dtype_code(copy.dtype) if copy is not None else 0, T, W, _stream())
+    return x, copy
+
+
+def head_prepare(rows: torch.Tensor, col0: int, wq: Optional[torch.Tensor], wk: Optional[torch.Tensor], eps: float,
+                 cos: Optional[torch.Tensor], sin: Optional[torch.Tensor], n_rot: int, temp_coef: float, temp_every: int,
+                 values_are_keys: bool, step, block_table: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                 n_heads: int, n_kv: int, head_dim: int, v_head_dim: int, write_cache: bool = True) -> torch.Tensor:
+    """Projected rows [.. | q | k | v | ..] (q at column col0; no v columns with ``values_are_keys``: a position's
+    value is its key as projected) -> q [T, heads * head_dim]; k and v into the token's page. Every q and k head is
+    divided by its root mean square (eps inside the root) and multiplied by wq / wk [head_dim] (None: no norm); then
+    channel pairs (2i, 2i + 1) below ``n_rot`` turn by the tables cos, sin [positions, n_rot / 2]; then q is multiplied
+    by 1 + temp_coef * ln(floor((position + 1) / temp_every) + 1) (temp_every 0: not)."""
+    _check(rows, "rows")
+    T, ld = rows.shape
+    nq, nk = n_heads * head_dim, n_kv * head_dim
+    nv = 0 if values_are_keys else n_kv * v_head_dim
+    if col0 < 0 or ld < col0 + nq + nk + nv:
+        raise KernelError("q, k and v lie outside the rows")
+    n_pages, ckv, page_size, chd = k_cache.shape
+    _check(k_cache, "k_cache", rows.dtype, (n_pages, n_kv, page_size, head_dim))
+    _check(v_cache, "v_cache", rows.dtype, (n_pages, n_kv, page_size, v_head_dim))
+    for name, w in (("wq", wq), ("wk", wk)):
+        if w is not None:
+            _check(w, name, torch.float32, (head_dim,))
+    if n_rot:
+        _check(cos, "cos", torch.float32)
+        _check(sin, "sin", torch.float32, cos.shape)
+        if cos.shape[1] != n_rot // 2:
+            raise KernelError(f"rotation tables must be [positions, {n_rot // 2}], got {tuple(cos.shape)}")
+    _check(block_table, "block_table", torch.int32)
+    q = torch.empty((T, nq), dtype=rows.dtype, device=rows.device)
+    f = _fn("post", "ib_head_prepare", [c_void_p, c_int64, c_int, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_int, c_float, c_int,
+                                        c_int, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int64] +
+            [c_int] * 6 + [c_int64, c_int, c_void_p, c_void_p])
+    _call(f, rows.data_ptr(), ld, int(col0), _ptr(wq), _ptr(wk), float(eps), _ptr(cos) if n_rot else None, _ptr(sin) if n_rot else None,
+          int(n_rot), float(temp_coef), int(temp_every), int(bool(values_are_keys)), step.positions.data_ptr(), step.token_seg.data_ptr(),
+          block_table.data_ptr(), block_table.shape[1], q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), T, n_heads, n_kv,
+          head_dim, v_head_dim, page_size, int(write_cache), n_pages, dtype_code(rows.dtype), _ptr(step.status), _stream())
+    return q
+
+
+def gate_mul(ctx: torch.Tensor, rows: torch.Tensor, gate_col: int) -> torch.Tensor:
+    """ctx[t, i] *= sigmoid(rows[t, gate_col + i]), in place; both in one storage dtype."""
+    _check(ctx, "ctx")
+    _check(rows, "rows", ctx.dtype)
+    T, W = ctx.shape
+    if rows.shape[0] != T or gate_col < 0 or gate_col + W > rows.shape[1]:
+        raise KernelError("the gate columns lie outside the rows")
+    f = _fn("post", "ib_gate_mul", [c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int, c_void_p])
+    _call(f, ctx.data_ptr(), rows.data_ptr(), rows.shape[1], int(gate_col), W, T, dtype_code(ctx.dtype), _stream())
+    return ctx
+
+
+def silu_rows(rows: torch.Tensor, col0: int, width: int) -> torch.Tensor:
+    """z * sigmoid(z) of columns [col0, col0 + width) of float32 rows, in place."""
+    _check(rows, "rows", torch.float32)
+    T, ld = rows.shape
+    if col0 < 0 or col0 + width > ld:
+        raise KernelError("the columns lie outside the rows")
+    f = _fn("post", "ib_silu_rows", [c_void_p, c_int64, c_int64, c_int64, c_int64, c_void_p])
+    _call(f, rows.data_ptr(), ld, int(col0), int(width), T, _stream())
+    return rows
+
+
+def shift_mix(x: torch.Tensor, last: torch.Tensor, mu: torch.Tensor, step, out_dtype: torch.dtype, write_state: bool = True) -> torch.Tensor:
+    """Mixtures of every token's row with the row of the token before it: out[m, t] = x[t] + (x[t - 1] - x[t]) * mu[m],
+    x float32 [T, W], mu float32 [n, W] -> [n, T, W] in ``out_dtype``. The row before a segment's first token is the
+    request's kept row ``last`` [slots, W] (zeros for a new request), which with ``write_state`` becomes the segment's last row."""
+    _check(x, "x", torch.float32)
+    T, W = x.shape
+    _check(mu, "mu", torch.float32)
+    n = mu.shape[0]
+    _check(mu, "mu", None, (n, W))
+    _check(last, "last", torch.float32)
+    if last.dim() != 2 or last.shape[1] != W:
+        raise KernelError(f"the kept rows must be [slots, {W}], got {tuple(last.shape)}")
+    out = torch.empty((n, T, W), dtype=out_dtype, device=x.device)
+    f = _fn("post", "ib_shift_mix", [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int64,
+                                     c_int, c_void_p])
+    _call(f, x.data_ptr(), last.data_ptr(), mu.data_ptr(), n, step.token_seg.data_ptr(), step.seg_start.data_ptr(), step.seg_slot.data_ptr(),
+          out.data_ptr(), dtype_code(out_dtype), T, W, int(write_state), _stream())
+    return out
+
+
+def double_exp_decay(rows: torch.Tensor, low_col: int, rank: int, up: torch.Tensor, bias: Optional[torch.Tensor]) -> torch.Tensor:
+    """decay[t, c] = exp(-exp(bias[c] + up[:, c] . tanh(rows[t, low_col : low_col + rank]))), float32 [T, C], with ``up``
+    float32 [rank, C] (a low rank's second factor, transposed)."""
+    _check(rows, "rows")
+    T, ld = rows.shape
+    _check(up, "up", torch.float32)
+    C = up.shape[1]
+    if up.shape[0] != rank or low_col < 0 or low_col + rank > ld:
+        raise KernelError("double_exp_decay: the low-rank columns lie outside the rows")
+    if bias is not None:
+        _check(bias, "bias", torch.float32, (C,))
+    decay = torch.empty((T, C), dtype=torch.float32, device=rows.device)
+    f = _fn("post", "ib_double_exp_decay", [c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p])
+    _call(f, rows.data_ptr(), ld, int(low_col), int(rank), up.data_ptr(), _ptr(bias), decay.data_ptr(), T, C, dtype_code(rows.dtype), _stream())
+    return decay
+
+
+GATE_ACTS = {None: 0, "silu": 1, "sigmoid": 2}
+
+
+def group_norm_gate(o: torch.Tensor, weight: Optional[torch.Tensor], eps: float, gate: Optional[torch.Tensor], gate_col: int,
+                    act: Optional[str], n_groups: int, size: int, out_dtype: torch.dtype) -> torch.Tensor:
+    """Per (token, group of ``size`` channels): o / sqrt(mean(o^2) + eps) * weight [groups * size] (None: no weight),
+    times act(gate logits) (columns gate_col + g * size of rows ``gate``, float32 or bfloat16; ``act`` "silu", "sigmoid"
+    or None for multipliers as they are) if given. o float32 [T, groups * size]."""
+    _check(o, "o", torch.float32)
+    T = o.shape[0]
+    _check(o, "o", None, (T, n_groups * size))
+    if weight is not None:
+        _check(weight, "weight", torch.float32, (n_groups * size,))
+    ldg = 0
+    if gate is not None:
+        _check(gate, "gate")
+        ldg = gate.shape[1]
+        if gate.shape[0] != T or gate_col < 0 or gate_col + n_groups * size > ldg:
+            raise KernelError("the gate columns lie outside the rows")
+    out = torch.empty((T, n_groups * size), dtype=out_dtype, device=o.device)
+    f = _fn("post", "ib_group_norm_gate", [c_void_p, c_void_p, c_float, c_void_p, c_int64, c_int64, c_int, c_int, c_void_p, c_int, c_int64,
+                                           c_int, c_int, c_void_p])
+    _call(f, o.data_ptr(), _ptr(weight), float(eps), _ptr(gate), ldg, int(gate_col), dtype_code(gate.dtype) if gate is not None else 0,
+          GATE_ACTS[act], out.data_ptr(), dtype_code(out_dtype), T, int(n_groups), int(size), _stream())
+    return out
+
+
+def relu_sq(x: torch.Tensor, col0: int = 0, width: Optional[int] = None) -> torch.Tensor:
+    """max(z, 0)^2, element by element, of columns [col0, col0 + width) of the rows x [T, ld] (default: all of them);
+    the result is contiguous [T, width]."""
+    _check(x, "x")
+    T, ld = x.shape
+    width = ld - col0 if width is None else int(width)
+    if col0 < 0 or width < 0 or col0 + width > ld:
+        raise KernelError("the activation's columns lie outside the rows")
+    out = torch.empty((T, width), dtype=x.dtype, device=x.device)
+    f = _fn("post", "ib_relu_sq", [c_void_p, c_int64, c_int64, c_int64, c_void_p, c_int64, c_int, c_void_p])
+    _call(f, x.data_ptr(), ld, int(col0), width, out.data_ptr(), T, dtype_code(x.dtype), _stream())
+    return out

@@ -26,6 +26,20 @@ Options beyond that, each a key of the part's spec (absent = off):
 ``sink``            a learned logit per head (role sink, [heads]) that enters the softmax denominator only
 ``names``           local tensor names by role (q, k, v, o, q_bias, k_bias, v_bias, q_filter, k_filter, v_filter, gate,
                     q_norm, k_norm, rel, sink) for checkpoints that call them otherwise
+
+A third group of options goes through one kernel that normalises per head, rotates, applies the temperature and
+fills the pages (``head_prepare``), then through the attention kernels that take a slope and kept first keys:
+
+``qk_head_norm_eps``   EVERY q head and every k head is divided by its own root mean square over head_dim and
+                       multiplied by a weight [head_dim] that the heads share (roles q_norm, k_norm), before any
+                       rotation; ``position`` may then be "rotary_interpolated" in the pairs layout (or none)
+``query_temperature``  {"coef": c, "every": n}: q at position p is multiplied by 1 + c ln(floor((p + 1) / n) + 1)
+``distance_slopes``    a number per head: slope_h * (i - j) is taken off the scaled score of query i and key j
+``keep_first``         with a window: query i also sees every key j < keep_first (at its true position)
+``values_are_keys``    there is no v matrix: a position's value is its key as projected, before norm and rotation
+``channel_gate``       the joined heads are multiplied, channel by channel, by sigmoid(x Wg^T) (role gate,
+                       [heads * v_head_dim, hidden]) before the output product; Wg rides in the q/k/v product
+``sink``               as above
 """
 from __future__ import annotations
 
@@ -108,7 +122,17 @@ class Attention(Mixer):
         self.prepared = (self.taps > 0 or self.value_norm_eps is not None or self.v_dim != self.head_dim or self.head_gate
                          or getattr(self.position, "layout", "half") == "pairs")
         # (row norms, distance bias and sink have a path of their own, decided below: its kernels ask for no other library)
-        own_path = spec.get("qk_row_norm_eps") is not None or spec.get("distance_bias") is not None or bool(spec.get("sink", False))
+        self.head_norm_eps = spec.get("qk_head_norm_eps")
+        self.q_temp = dict(spec["query_temperature"]) if spec.get("query_temperature") else None
+        self.slopes = [float(v) for v in spec["distance_slopes"]] if spec.get("distance_slopes") is not None else None
+        self.keep_first = int(spec.get("keep_first") or 0)
+        self.values_are_keys = bool(spec.get("values_are_keys", False))
+        self.channel_gate = bool(spec.get("channel_gate", False))
+        self.per_head = (self.head_norm_eps is not None or self.q_temp is not None or self.slopes is not None or self.keep_first > 0
+                         or self.values_are_keys or self.channel_gate)
+        if self.per_head:
+            self._check_per_head(spec)
+        own_path = self.per_head or spec.get("qk_row_norm_eps") is not None or spec.get("distance_bias") is not None or bool(spec.get("sink", False))
         if self.prepared and not own_path:
             if max(self.head_dim, self.v_dim) > ops.qkv_prepare_max_head_dim():
                 raise ValueError(f"the prepare kernel takes head sizes up to {ops.qkv_prepare_max_head_dim()}, "
@@ -119,7 +143,9 @@ class Attention(Mixer):
         self.distance_bias = spec.get("distance_bias")
         self.has_sink = bool(spec.get("sink", False))
         self.row_norm = self.row_norm_eps is not None
-        if self.row_norm or self.distance_bias is not None or self.has_sink:
+        if self.per_head:
+            self.prepared = self.biased = False
+        elif self.row_norm or self.distance_bias is not None or self.has_sink:
             # these scores are not the ones the fast kernels compute; the projected rows go through the row-norm kernel
             if self.taps > 0 or self.position is not None or self.value_norm_eps is not None or self.head_gate:
                 raise ValueError("row norms, distance bias and sinks do not combine with filters, rotation, value norm or head gates")
@@ -129,11 +155,29 @@ class Attention(Mixer):
             self.biased = True
         else:
             self.biased = False
-        self.q_norm_w = self.k_norm_w = self.bias_table = self.bias_by_head = self.sink_w = None
-        self.n_qkv = (self.n_heads + self.n_kv) * self.head_dim + self.n_kv * self.v_dim
+        self.q_norm_w = self.k_norm_w = self.bias_table = self.bias_by_head = self.sink_w = self.slopes_w = None
+        self.n_qkv = (self.n_heads + self.n_kv) * self.head_dim + (0 if self.values_are_keys else self.n_kv * self.v_dim)
         self.qkv: Optional[Linear] = None
         self.o: Optional[Linear] = None
         self.filter_w = None
+
+    def _check_per_head(self, spec):
+        if self.taps > 0 or self.value_norm_eps is not None or self.head_gate or self.qkv_bias or spec.get("qk_row_norm_eps") is not None \
+                or spec.get("distance_bias") is not None:
+            raise ValueError("per-head norms, temperature, slopes, kept first keys, keys as values and channel gates do not combine "
+                             "with filters, value norm, head gates, biases, row norms or a distance table")
+        if self.head_norm_eps is not None and float(self.head_norm_eps) <= 0:
+            raise ValueError("qk_head_norm_eps must be positive")
+        if self.position is not None and (getattr(self.position, "layout", None) != "pairs" or self.position.rotary_tables is None):
+            raise ValueError("this attention rotates channel pairs from tables (position kind 'rotary_interpolated' or 'rotary_pairs' in the pairs layout)")
+        if self.q_temp is not None and (int(self.q_temp.get("every", 0)) <= 0 or "coef" not in self.q_temp):
+            raise ValueError("query_temperature needs 'coef' and a positive 'every'")
+        if self.slopes is not None and len(self.slopes) != self.n_heads:
+            raise ValueError(f"distance_slopes needs one number per head ({self.n_heads}), got {len(self.slopes)}")
+        if self.keep_first < 0 or (self.keep_first > 0 and self.window is None):
+            raise ValueError("keep_first goes with a window")
+        if self.values_are_keys and self.v_dim != self.head_dim:
+            raise ValueError("values that are the keys have the keys' size")
 
     @classmethod
     def param_shapes(cls, spec):
@@ -141,6 +185,12 @@ class Attention(Mixer):
         vd = int(spec.get("v_head_dim") or hd)
         n = _names(spec)
         shapes = {n["q"]: (nh * hd, H), n["k"]: (nkv * hd, H), n["v"]: (nkv * vd, H), n["o"]: (H, nh * vd)}
+        if spec.get("values_are_keys", False):
+            del shapes[n["v"]]
+        if spec.get("channel_gate", False):
+            shapes[n["gate"]] = (nh * vd, H)
+        if spec.get("qk_head_norm_eps") is not None:
+            shapes.update({n["q_norm"]: (hd,), n["k_norm"]: (hd,)})
         if spec.get("qkv_bias", False):
             shapes.update({n["q_bias"]: (nh * hd,), n["k_bias"]: (nkv * hd,), n["v_bias"]: (nkv * vd,)})
         taps = int(spec.get("filter_taps") or 0)
@@ -173,8 +223,8 @@ class Attention(Mixer):
 
     def load(self, params):
         n = _names(self.spec)
-        mats = [params[n["q"]], params[n["k"]], params[n["v"]]]
-        if self.head_gate:
+        mats = [params[n["q"]], params[n["k"]]] + ([] if self.values_are_keys else [params[n["v"]]])
+        if self.head_gate or self.channel_gate:
             mats.append(params[n["gate"]])
         w = torch.cat(mats, dim=0)
         if self.head_gate and w.shape[0] % 8:
@@ -188,6 +238,16 @@ class Attention(Mixer):
         self.qkv = Linear(self.rt, w, b)
         self.o = Linear(self.rt, params[n["o"]])
         f32 = dict(device=self.rt.device, dtype=torch.float32)
+        if self.head_norm_eps is not None:
+            self.q_norm_w, self.k_norm_w = params[n["q_norm"]].to(**f32).contiguous(), params[n["k_norm"]].to(**f32).contiguous()
+        if self.slopes is not None:
+            self.slopes_w = torch.tensor(self.slopes, **f32)
+            # for the tensor-core kernel of prompt portions: a row per head of -slope * distance / scale, as long as the
+            # engine's longest sequence (it is added to the raw score); left out where it would be large
+            L = int(self.rt.max_seq_len or 0)
+            if self.rt.fast("attention") and self.scale > 0 and self.v_dim == self.head_dim and 0 < L * self.n_heads <= (1 << 24):
+                dist = torch.arange(L, dtype=torch.float64)
+                self.bias_by_head = (-torch.tensor(self.slopes, dtype=torch.float64)[:, None] * dist[None, :] / self.scale).to(**f32).contiguous()
         if self.row_norm:
             self.q_norm_w, self.k_norm_w = params[n["q_norm"]].to(**f32).contiguous(), params[n["k_norm"]].to(**f32).contiguous()
         if self.distance_bias is not None:
@@ -202,7 +262,8 @@ class Attention(Mixer):
                 .to(device=self.rt.device, dtype=torch.float32).t().contiguous()
 
     def cache_need(self):
-        pages = PagedKVNeed(self.n_kv, self.head_dim, self.window, None if self.v_dim == self.head_dim else self.v_dim)
+        pages = PagedKVNeed(self.n_kv, self.head_dim, self.window, None if self.v_dim == self.head_dim else self.v_dim,
+                            keep_first=self.keep_first if self.window is not None else 0)
         if self.taps > 1:
             # the last taps - 1 projected rows of the request, in the compute dtype (copies, not sums)
             return CompositeNeed({"pages": pages, "tails": StateNeed({"qkv": ((self.taps - 1, self.n_qkv), None)})})
@@ -226,7 +287,7 @@ class Attention(Mixer):
     def input_product(self):
         """The q/k/v(/gate) product, for a block that joins the products of parts reading the same rows. Only the
         prepared path reads its rows by (leading dimension, first column)."""
-        return (self.qkv, "compute") if (self.prepared or self.biased) else None
+        return (self.qkv, "compute") if (self.prepared or self.biased or self.per_head) else None
 
     def drop_input_product(self):
         self.qkv = None
@@ -246,7 +307,36 @@ class Attention(Mixer):
                                       self.head_dim, self.window, self.scale, step.status, self.v_dim, self.bias_table, self.sink_w)
         return self._project_out(ctx, residual)
 
+    def _forward_per_head(self, qkv, col0, step, cache, residual, write_cache):
+        """Per-head norms, pair rotation, the queries' temperature and the cache write in one kernel; attention whose
+        scores lose a slope times the distance, whose window keeps the first keys and whose denominator takes the sink;
+        the gate per channel. The part's columns [q | k | (v) | gate] start at ``col0`` of the rows ``qkv``."""
+        table = step.block_tables[cache.group]
+        cos = sin = None
+        n_rot = 0
+        if self.position is not None:
+            cos, sin = self.position.rotary_tables(self.rt.max_seq_len)
+            n_rot = self.position.rotary_dims
+        coef, every = (float(self.q_temp["coef"]), int(self.q_temp["every"])) if self.q_temp is not None else (0.0, 0)
+        q = ops.head_prepare(qkv, col0, self.q_norm_w, self.k_norm_w, float(self.head_norm_eps or 0.0), cos, sin, n_rot, coef, every,
+                             self.values_are_keys, step, table, cache.k, cache.v, self.n_heads, self.n_kv, self.head_dim, self.v_dim,
+                             write_cache)
+        ctx = None
+        if self.rt.fast("attention"):
+            ctx = ops.attention_window(q, cache.k, cache.v, table, step, self.n_heads, self.n_kv, self.head_dim, self.v_dim,
+                                       self.window, self.scale, None, self.sink_w, self.bias_by_head, self.keep_first, self.slopes_w)
+        if ctx is None:
+            ctx = ops.attention_plain(q, cache.k, cache.v, table, step.token_seg, step.positions, self.n_heads, self.n_kv,
+                                      self.head_dim, self.window, self.scale, step.status, self.v_dim, None, self.sink_w,
+                                      keep_first=self.keep_first, slopes=self.slopes_w)
+        if self.channel_gate:
+            ops.gate_mul(ctx, qkv, col0 + self.n_qkv)
+        return self._project_out(ctx, residual)
+
     def forward(self, x, step, cache, residual, write_cache=True):
+        if self.per_head:
+            qkv, col0 = own_or_projected(self, x, self.qkv)
+            return self._forward_per_head(qkv, col0, step, cache, residual, write_cache)
         if self.biased:
             qkv, col0 = own_or_projected(self, x, self.qkv)
             return self._forward_biased(qkv, col0, step, cache, residual, write_cache)

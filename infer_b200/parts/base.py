@@ -30,6 +30,7 @@ class PagedKVNeed:
     values_in_keys: bool = False      # True: a position's value is the first v_head_dim channels of its key row (one
                                       # row per position serves both, as in attention through a shared latent); there
                                       # are no value pages and the view's ``v`` is None
+    keep_first: int = 0               # with a window: the positions below this stay readable for every later query
 
     @property
     def value_dim(self) -> int:
@@ -157,6 +158,9 @@ class PositionEncoding(Part):
 
 class Mixer(Part):
     accepts_deferred_norm = False    # True: forward() may get a DeferredNorm as x
+    # True: a block whose sublayers read the residual stream itself hands forward() the float32 rows of the stream as x,
+    # whatever the compute dtype (a mixer that combines rows in float32 before its first matrix product)
+    reads_stream = False
 
     def cache_need(self):
         """PagedKVNeed, StateNeed, CompositeNeed or None."""

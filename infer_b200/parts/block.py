@@ -12,7 +12,13 @@ the residual sum are one float32 kernel.
 "sublayer_norm": the sublayers read the residual stream h itself and the norm sits on what they RETURN:
 h += norm_a(mixer(h)); h += norm_b(feed_forward(h)); the feed-forward and its norm may be absent. Slots: mixer,
 mixer_out_norm, feed_forward, feed_forward_out_norm. Norm and sum are one float32 kernel, which also leaves h in the
-compute dtype for the next sublayer's first matrix product."""
+compute dtype for the next sublayer's first matrix product.
+
+"postnorm": the norm comes AFTER the sum and its result IS the stream: h <- norm_a(alpha h + mixer(h));
+h <- norm_b(alpha h + feed_forward(h)), with the constant ``residual_scale`` = alpha (an option of the layer's spec);
+the feed-forward and its norm may be absent. Slots: mixer, mixer_norm, feed_forward, feed_forward_norm. The sublayers
+read h itself. Scaling, sum and norm are one float32 kernel (two mixers side by side hand over both results and their
+constants), which also leaves h in the compute dtype for the next sublayer's first matrix product."""
 from __future__ import annotations
 
 import os
@@ -180,3 +186,49 @@ class SublayerNormBlock(Block):
         if have is not None and have[0] is h and have[1] is not None and have[1].dtype == dtype:
             return have[1]
         return ops.cast_rows(h, dtype)
+
+
+@register_block("postnorm")
+class PostNormBlock(Block):
+    def __init__(self, mixer, mixer_norm, feed_forward=None, feed_forward_norm=None, residual_scale: float = 1.0):
+        parts = {"mixer": mixer, "mixer_norm": mixer_norm}
+        if feed_forward is not None:
+            if feed_forward_norm is None:
+                raise ValueError("a feed-forward in a postnorm block needs its norm")
+            parts.update(feed_forward=feed_forward, feed_forward_norm=feed_forward_norm)
+        super().__init__(**parts)
+        self.feed_forward, self.feed_forward_norm = feed_forward, feed_forward_norm
+        self.alpha = float(residual_scale)
+        for n in (mixer_norm, feed_forward_norm):
+            if n is not None and not getattr(n, "fusable", False):
+                raise ValueError("a postnorm block needs norms of the (weight, eps) root-mean-square kind")
+
+    def forward(self, h, step, cache, write_cache=True):
+        from .. import ops
+        rt = self.mixer.rt
+        x = h if (rt.dtype == torch.float32 or self.mixer.reads_stream) else SublayerNormBlock._copy_of(h, step, rt.dtype)
+        norm = self.mixer_norm
+        sides = getattr(self.mixer, "forward_sides", None)
+        if sides is not None and not getattr(self.mixer, "normed", False):
+            # In a decode step every kernel is a few microseconds of latency: two mixers side by side run on two streams
+            side = _side_streams(h.device)[0] if (PARALLEL_BRANCHES and step.decode_only and rt.dtype != torch.float32) else None
+            if side is not None:
+                main = torch.cuda.current_stream(h.device)
+                fork = torch.cuda.Event()
+                fork.record(main)
+                side.wait_event(fork)
+            a, b, sa, sb = sides(x, step, cache, write_cache, side)
+            if side is not None:
+                done = torch.cuda.Event()
+                done.record(side)
+                main.wait_event(done)
+            h, copy = ops.sum_norm(h, self.alpha, a, sa, b, sb, norm.weight, norm.eps, rt.dtype)
+        else:
+            y = self.mixer.forward(x, step, cache, None, write_cache)
+            h, copy = ops.sum_norm(h, self.alpha, y, 1.0, None, 0.0, norm.weight, norm.eps, rt.dtype)
+        if self.feed_forward is not None:
+            y = self.feed_forward.forward(copy if copy is not None else h, None)
+            norm = self.feed_forward_norm
+            h, copy = ops.sum_norm(h, self.alpha, y, 1.0, None, 0.0, norm.weight, norm.eps, rt.dtype)
+        step.extras["rows_copy"] = (h, copy)
+        return h

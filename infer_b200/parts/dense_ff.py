@@ -1,7 +1,7 @@
 """Dense feed-forward with one hidden layer: out = residual + act(x Wup^T) Wdown^T, no biases; with ``gated`` the
 hidden layer is act(x Wgate^T) * (x Wup^T) (gate and up are one matrix product).
 
-``activation``: "gelu_tanh" is 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))).  ``names`` renames the matrices
+``activation``: "gelu_tanh" is 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))); "relu_squared" is max(z, 0)^2.  ``names`` renames the matrices
 (roles up, down, gate).
 """
 from __future__ import annotations
@@ -13,7 +13,7 @@ from ..config.specs import PartSpec
 from .base import FeedForward, own_or_projected, register_feed_forward
 from .linear import Linear
 
-_ACTIVATIONS = {"gelu_tanh": ops.gelu_tanh}        # each: (rows, first column, width) -> contiguous [T, width]
+_ACTIVATIONS = {"gelu_tanh": ops.gelu_tanh, "relu_squared": ops.relu_sq}        # each: (rows, first column, width) -> contiguous [T, width]
 _NAMES = {"up": "up_proj.weight", "down": "down_proj.weight", "gate": "gate_proj.weight"}
 
 

@@ -52,14 +52,15 @@ class Linear:
         return cls(rt, torch.cat(mats, dim=0), torch.cat(biases) if any_bias else None), starts
 
     def __call__(self, x: torch.Tensor, residual: Optional[torch.Tensor] = None,
-                 out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+                 out_dtype: Optional[torch.dtype] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
         """x [rows, in] in the compute dtype (or a DeferredNorm of float32 rows). With ``residual`` (float32 [rows, out]) the result is
         float32 and is written over ``residual``. Otherwise the result has ``out_dtype`` (default:
-        the compute dtype)."""
+        the compute dtype), and is written into ``out`` (contiguous [rows, out] of that dtype) if given."""
         from .base import DeferredNorm
-        out = residual
         if residual is not None:
-            out_dtype = torch.float32
+            out, out_dtype = residual, torch.float32
+        elif out is not None:
+            out_dtype = out.dtype
         if self.rt.fast("linear"):
             from .. import fast_ops
             y = fast_ops.linear(x, self.weight, self.bias, residual, out_dtype or self.rt.dtype, out)

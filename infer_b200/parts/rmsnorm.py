@@ -1,6 +1,7 @@
 """RMSNorm: y = x * rsqrt(mean(x^2) + eps) * w; eps inside the root, added after the mean; no mean
 subtraction, no bias, the weight multiplies as it is (src/forward.cpp:21-31, kernels/ops/rmsnorm.cu:9-28).
-``weight_name`` in the spec renames the one tensor (default "weight") under the part's prefix."""
+``weight_name`` in the spec renames the one tensor (default "weight") under the part's prefix. ``weight_offset``
+(default 0) is added to the stored weight when it is loaded: a design whose norms multiply by (1 + w) stores w around zero."""
 from __future__ import annotations
 
 from typing import Optional
@@ -22,6 +23,7 @@ class RMSNorm(Norm):
     def __init__(self, spec: PartSpec, runtime):
         super().__init__(spec, runtime)
         self.size, self.eps = int(spec["size"]), float(spec["eps"])
+        self.offset = float(spec.get("weight_offset") or 0.0)
         if self.size <= 0 or self.eps <= 0:
             raise ValueError("rmsnorm needs a positive size and eps")
         self.weight = None
@@ -32,10 +34,12 @@ class RMSNorm(Norm):
 
     @classmethod
     def init_params(cls, spec, name, shape, gen):
-        return 1.0 + 0.1 * torch.randn(shape, generator=gen, dtype=torch.float32, device=gen.device)
+        return 1.0 - float(spec.get("weight_offset") or 0.0) + 0.1 * torch.randn(shape, generator=gen, dtype=torch.float32, device=gen.device)
 
     def load(self, params):
         self.weight = params[str(self.spec.get("weight_name", "weight"))].to(device=self.rt.device, dtype=torch.float32).contiguous()
+        if self.offset:
+            self.weight = (self.weight + self.offset).contiguous()
 
     def forward(self, x: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
                 rows: Optional[torch.Tensor] = None) -> torch.Tensor:

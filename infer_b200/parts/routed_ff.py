@@ -22,8 +22,11 @@ Other forms, each a key of the spec:
 
 ``router_kind``  "softmax_groups" (above) or "sigmoid": s = sigmoid(x Wr^T); the ``top`` experts with the largest
                  s + correction are chosen (``correction`` [experts], a stored tensor that only the choice sees);
-                 weight_e = s_e as it is, not renormalised; no groups
-``expert_kind``  "clipped_swish_glu" (above) or "relu_squared": expert(x) = Wd relu(Wu x)^2, no gate matrix, no limit
+                 weight_e = s_e as it is, not renormalised; no groups. "softmax_top": the ``top`` experts with the
+                 largest logits are chosen and their weights are the softmax over the chosen logits only (which is
+                 what the form above gives without groups and with sum_eps 0); no groups
+``expert_kind``  "clipped_swish_glu" (above), "relu_squared": expert(x) = Wd relu(Wu x)^2, no gate matrix, no limit, or
+                 "swish_glu": expert(x) = Wd (g sigmoid(g) * u) with g = Wg x, u = Wu x, no limit
 ``out_scale``    a constant on the result (default 1), multiplied into the experts' weights in float32: a block's
                  residual multiplier costs nothing this way
 """
@@ -50,7 +53,12 @@ class RoutedExperts(FeedForward):
         self.router_kind = str(spec.get("router_kind", "softmax_groups"))
         self.expert_kind = str(spec.get("expert_kind", "clipped_swish_glu"))
         self.out_scale = float(spec.get("out_scale", 1.0))
-        if self.router_kind not in ("softmax_groups", "sigmoid") or self.expert_kind not in ("clipped_swish_glu", "relu_squared"):
+        if self.router_kind == "softmax_top":
+            if self.groups != 1 or self.keep != 1:
+                raise ValueError("a softmax_top router has no groups")
+            self.sum_eps = 0.0
+        if self.router_kind not in ("softmax_groups", "sigmoid", "softmax_top") or \
+                self.expert_kind not in ("clipped_swish_glu", "relu_squared", "swish_glu"):
             raise ValueError(f"routed_experts: unknown router_kind {self.router_kind!r} or expert_kind {self.expert_kind!r}")
         if self.router_kind == "sigmoid" and (self.groups != 1 or self.keep != 1):
             raise ValueError("a sigmoid router has no groups")
@@ -113,8 +121,8 @@ class RoutedExperts(FeedForward):
                 raise NotImplementedError("a shared expert of the relu_squared form")
             act = ops.scaled_relu_sq(rows, weights, self.ff)
         else:
-            act = ops.glu_act(rows, 0, self.width, self.width, "clipped_swish", self.limit, self.shared_limit, self.slope,
-                              weights, self.ff, self.n_experts)
+            act = ops.glu_act(rows, 0, self.width, self.width, "swish" if self.expert_kind == "swish_glu" else "clipped_swish",
+                              self.limit, self.shared_limit, self.slope, weights, self.ff, self.n_experts)
         if residual is None:
             return self.down(act, out_dtype=torch.float32)
         return self.down(act, residual=residual)
