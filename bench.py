@@ -5,6 +5,7 @@ random weights on one B200.
     python bench.py --design ruvenex [--sizes 1.5b|7b] [--layers L]     (another design beside Qwen2 at equal sizes)
     python bench.py --design fozerax [--sizes 1.5b|7b] [--layers L]     (beside Ruvenex, the closest design, and Qwen2)
     python bench.py --design pefazen [--sizes 1.5b|7b] [--layers L]     (beside Fozerax, the closest design, and Qwen2)
+    python bench.py --design biravik [--sizes 1.5b|7b] [--layers L]     (beside Fozerax, the closest design, and Qwen2)
 
 Prints ONE JSON line. "value" is decoded tokens per second of the step function, timed on the device with CUDA
 events around K decode steps of a batch of 8 requests whose 2,048-token contexts already lie in the paged cache
@@ -36,9 +37,9 @@ def _preset(name):
 SIZES = {"1.5b": _preset("qwen2.5-1.5b"), "7b": _preset("qwen2.5-7b"), "14b": _preset("qwen2.5-14b")}
 # Other designs at the same layer sizes (width, heads, feed-forward), for --design.
 DESIGNS = {"ruvenex": {"1.5b": "ruvenex-1.5b", "7b": "ruvenex-7b"}, "fozerax": {"1.5b": "fozerax-1.5b", "7b": "fozerax-7b"},
-           "pefazen": {"1.5b": "pefazen-1.5b", "7b": "pefazen-7b"}}
+           "pefazen": {"1.5b": "pefazen-1.5b", "7b": "pefazen-7b"}, "biravik": {"1.5b": "biravik-1.5b", "7b": "biravik-7b"}}
 # the designs a design is measured beside, besides Qwen2: the closest one the engine has
-BESIDE = {"fozerax": ["ruvenex"], "pefazen": ["fozerax"]}
+BESIDE = {"fozerax": ["ruvenex"], "pefazen": ["fozerax"], "biravik": ["fozerax"]}
 CONFIG = SIZES["1.5b"]
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
@@ -415,6 +416,37 @@ def pefazen_flops(cfg, T):
     return total + 2 * W * cfg["vocab"]
 
 
+def biravik_flops(cfg, T):
+    """Arithmetic of a prompt of T tokens through a Biravik configuration as the design states it: the projections,
+    attention scores and sums over what a query sees (a window and the kept first keys, or everything before it), the
+    recurrences' state updates and read-outs, and the chosen experts only."""
+    W, total = cfg["width"], 0.0
+
+    def softmax_side(a, shared_values):
+        n = (a["heads"] + a["kv_heads"]) * a["dim"] + (0 if shared_values else a["kv_heads"] * a["vdim"]) + 2 * a["heads"] * a["vdim"]
+        mask = a.get("mask")
+        win = min(T, mask["size"]) if mask else T
+        seen = T * win - win * (win - 1) / 2 + (max(0, T - win) * min(mask.get("keep_first", 0), T) if mask else 0)
+        return 2 * T * W * n + 2 * a["heads"] * (a["dim"] + a["vdim"]) * seen
+    for l in cfg["layers"]:
+        m = l["mixer"]
+        if l["type"] == "attention":
+            total += softmax_side(m, True)
+        elif l["type"] == "parallel":
+            r = m["right"]
+            total += softmax_side(m["left"], False)
+            total += 2 * T * W * (2 * r["heads"] * r["dim"] + 3 * r["heads"] * r["vdim"]) + T * r["heads"] * r["dim"] * r["vdim"] * 4
+        else:
+            C, rank = m["heads"] * m["dim"], m.get("rank", 64)
+            total += 2 * T * W * (5 * C + rank) + 2 * T * C * rank + T * C * m["dim"] * 6
+        f = l["mlp"]
+        if f and f["kind"] == "dense":
+            total += 2 * T * W * 2 * f["ff"]
+        elif f:
+            total += 2 * T * W * (3 * f["router"]["top"] * f["expert"]["ff"] + f["router"]["experts"])
+    return total + 2 * W * cfg["vocab"]
+
+
 def design_flops(cfg, T):
     """Arithmetic of a prompt of T tokens through a model of --design's configuration (matrix products, attention
     scores and sums, the recurrence's state updates and read-outs), logits at the last place only."""
@@ -422,6 +454,8 @@ def design_flops(cfg, T):
         return fozerax_flops(cfg, T)
     if cfg.get("architecture") == "Pefazen":
         return pefazen_flops(cfg, T)
+    if cfg.get("architecture") == "Biravik":
+        return biravik_flops(cfg, T)
     W, total = cfg["width"], 0.0
     for l in cfg["layers"]:
         a, r = l["mixer"]["left"], l["mixer"]["right"]
