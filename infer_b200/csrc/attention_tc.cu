@@ -200,6 +200,11 @@ struct Params {
     // a logit without key or value that enters the softmax denominator once (the part that holds the first keys counts it).
     const float* bias; int bias_len;
     const float* sink;
+    // Optional. keep_first > 0 (with a window): every query also sees the keys at positions below keep_first; the key
+    // tiles that hold such keys and lie wholly before the window's first tile come first in a query tile's list of
+    // tiles. slopes [heads]: slopes[h] * (i - j) is taken off the scaled score (one multiply-add per score).
+    int keep_first;
+    const float* slopes;
 };
 constexpr int MAX_SPLIT = 4;
 constexpr int PART_MIN_TILES = 4;
@@ -235,11 +240,15 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
     const int lo_key = p.window > 0 ? max(0, q_first - p.window + 1) : 0;
     // this CTA's key tiles: all of the query tile's, or one of `n_parts` contiguous shares
     const int all0 = lo_key / BN, all1 = q_last / BN;
-    const int n_all = all1 - all0 + 1;
+    const int keep_end = min(p.keep_first, lo_key);      // keys below it are seen although the window has passed them
+    const int n_keep = min((keep_end + BN - 1) / BN, all0);   // tiles of kept keys wholly before the window's first tile
+    const int n_all = n_keep + all1 - all0 + 1;
     const int n_parts = max(1, min(p.split, n_all / PART_MIN_TILES));
     if (part >= n_parts) return;
-    const int kt0 = all0 + (n_all * part) / n_parts, kt1 = all0 + (n_all * (part + 1)) / n_parts - 1;
-    const int n_tiles = kt1 - kt0 + 1;                   // >= PART_MIN_TILES when the tile is shared, >= 1 otherwise
+    // a CTA's tiles are numbered along the list [kept tiles | the window's tiles]
+    const int lt0 = (n_all * part) / n_parts, lt1 = (n_all * (part + 1)) / n_parts - 1;
+    const int n_tiles = lt1 - lt0 + 1;                   // >= PART_MIN_TILES when the tile is shared, >= 1 otherwise
+    auto tile_of = [&](int j) -> int { const int lt = lt0 + j; return lt < n_keep ? lt : all0 + lt - n_keep; };
     // Scratch is laid out over the segments that have two or more tokens only (a step may carry dozens of one-token
     // segments beside one portion): this segment's rank among those, counted from the segment table.
     int tile_id = 0;
@@ -252,18 +261,18 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
     // The page ids of this CTA's key range, checked, in shared memory (a read of the table in global memory costs the
     // producer a round trip to L2 per page otherwise); ranges longer than the array fall back to the table itself.
     __shared__ int page_tab[TAB_MAX];
-    const int tab0 = kt0 * PAGES_PER_TILE, tab_n = (kt1 + 1) * PAGES_PER_TILE - tab0;
+    const int tab_n = n_tiles * PAGES_PER_TILE;
     const bool tab_ok = tab_n <= TAB_MAX;
     if (tab_ok) {
         for (int i = threadIdx.x; i < tab_n; i += NUM_THREADS) {
-            const int idx = tab0 + i;
+            const int idx = tile_of(i / PAGES_PER_TILE) * PAGES_PER_TILE + i % PAGES_PER_TILE;
             const int page = idx < p.max_blocks ? table[idx] : -1;
             page_tab[i] = (page < 0 || page >= p.n_pages) ? -1 : page;
         }
     }
-    auto page_of = [&](int key) -> int {                 // page id of the page that holds `key`, or -1
+    auto page_of = [&](int j, int key) -> int {          // page id of the page that holds `key` of this CTA's tile j, or -1
         const int idx = key / PAGE;
-        if (tab_ok) return page_tab[idx - tab0];
+        if (tab_ok) return page_tab[j * PAGES_PER_TILE + idx % PAGES_PER_TILE];
         if (idx >= p.max_blocks) return -1;
         const int page = table[idx];
         return (page < 0 || page >= p.n_pages) ? -1 : page;
@@ -301,14 +310,14 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         // Loads the K (which = 0) or V (which = 1) pages of tile j. Pages that hold nothing this step may read are
         // skipped (their rows are masked, and zeroed for V).
         auto load_tile = [&](int j, int which) {
-            const int key0 = (kt0 + j) * BN;
+            const int key0 = tile_of(j) * BN;
             const uint32_t full = (which ? v_full : k_full) + 8 * (j & 1);
             const uint32_t dst0 = which ? v_s + (j & 1) * V_BYTES : k_s + (j & 1) * K_BYTES;
             int page = -1;
             if (lane < PAGES_PER_TILE) {
                 const int key = key0 + lane * PAGE;
-                page = key <= last_written ? page_of(key) : -1;
-                if (key <= last_written && key + PAGE - 1 >= lo_key && page < 0) atomicExch(p.status, STATUS_BAD_PAGE);
+                page = key <= last_written ? page_of(j, key) : -1;
+                if (key <= last_written && (key + PAGE - 1 >= lo_key || key < keep_end) && page < 0) atomicExch(p.status, STATUS_BAD_PAGE);
             }
             const int valid = __popc(__ballot_sync(0xffffffffu, page >= 0));
             if (lane == 0) {
@@ -406,9 +415,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
             l = 1.0f;
         }
         const float* bias_h = p.bias ? p.bias + int64_t(h) * p.bias_len : nullptr;
+        const float slope_raw = p.slopes ? p.slopes[h] * LOG2E / p.scale_log2 : 0.0f;      // on the raw score: slope / scale
         bool ok = true;
         for (int j = 0; j < n_tiles; j++) {
-            const int key0 = (kt0 + j) * BN;
+            const int key0 = tile_of(j) * BN;
             IB_T(j, 0);
             ok = !slots[1] && mbar_wait(s_full + 8 * (j & 1), (j >> 1) & 1);
             ok = __all_sync(0xffffffffu, ok);
@@ -426,7 +436,13 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
 #pragma unroll
                 for (int c = 0; c < BN; c++) s[c] += __ldg(bias_h + min(max(d0 - c, 0), top));
             }
-            const bool full_tile = key0 + BN - 1 <= q_first && key0 >= (p.window > 0 ? max(0, q_first + BM - 1 - p.window + 1) : 0);
+            if (p.slopes) {
+                const float d0 = float(row_pos - key0);
+#pragma unroll
+                for (int c = 0; c < BN; c++) s[c] = fmaf(-slope_raw, d0 - float(c), s[c]);
+            }
+            const bool full_tile = key0 + BN - 1 <= q_first &&
+                                   (key0 >= (p.window > 0 ? max(0, q_first + BM - 1 - p.window + 1) : 0) || key0 + BN - 1 < p.keep_first);
             // Raw scores: the scale goes into the exponent's multiply-add below. Most tiles lie wholly below the diagonal
             // and inside the window and need no mask. (Masks are written without short-circuit operators: a branch per
             // element costs more than the arithmetic.)
@@ -436,10 +452,11 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
 #pragma unroll
                 for (int c = 0; c < BN; c++) mxs[c & 3] = fmaxf(mxs[c & 3], s[c]);
             } else {
-                const int hi = row_pos - key0, lo = row_lo - key0;       // visible: lo <= c <= hi
+                const int hi = row_pos - key0, lo = row_lo - key0;       // visible: lo <= c <= hi, or c <= hi among the kept first keys
+                const int kept = p.keep_first - key0;
 #pragma unroll
                 for (int c = 0; c < BN; c++) {
-                    const bool vis = (c <= hi) & (c >= lo);
+                    const bool vis = (c <= hi) & ((c >= lo) | (c < kept));
                     s[c] = vis ? s[c] : -INFINITY;
                     mxs[c & 3] = fmaxf(mxs[c & 3], s[c]);
                 }
@@ -497,7 +514,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
                 for (int u = r; u < BN * DB; u += BM) {
                     const int key_row = u % BN, db = u / BN;
                     const int key = key0 + key_row;
-                    if (key > last_written || page_of(key) < 0) {
+                    if (key > last_written || page_of(j, key) < 0) {
                         uint4* line = reinterpret_cast<uint4*>(v_ptr + (j & 1) * V_BYTES + db * (BN * 128) + key_row * 128);
 #pragma unroll
                         for (int e = 0; e < 8; e++) line[e] = make_uint4(0u, 0u, 0u, 0u);
@@ -624,8 +641,9 @@ static int prefill_tc(const void* q, const void* k_cache, const void* v_cache, v
                       int n_heads, int n_kv, int head_dim, int page_size, int window, float scale, int64_t n_pages,
                       int max_q_len, int* status, cudaStream_t stream, int split, float* workspace,
                       int64_t workspace_floats, unsigned int* counters, int64_t n_counters, int n_long_segments,
-                      const float* bias, int bias_len, const float* sink) {
+                      const float* bias, int bias_len, const float* sink, int keep_first = 0, const float* slopes = nullptr) {
     if (n_segments <= 0 || max_q_len <= 1) return IB_OK;
+    if (slopes && !(scale > 0.0f)) return ib::fail(IB_ERR_ARG, "attention_tc: slopes need a positive scale");
     if (bias && (bias_len <= 0 || !(scale > 0.0f))) return ib::fail(IB_ERR_ARG, "attention_tc: a distance bias needs rows and a positive scale");
     if (head_dim != HD) return ib::fail(IB_ERR_ARG, "attention_tc: built for head_dim %d, called with %d", HD, head_dim);
     if (page_size != PAGE) return ib::fail(IB_ERR_ARG, "attention_tc: pages must hold %d positions, got %d", PAGE, page_size);
@@ -652,6 +670,7 @@ static int prefill_tc(const void* q, const void* k_cache, const void* v_cache, v
     p.n_heads = n_heads; p.n_kv = n_kv; p.group = n_heads / n_kv; p.window = window; p.scale_log2 = scale * LOG2E;
     p.n_pages = n_pages; p.status = status;
     p.bias = bias; p.bias_len = bias_len; p.sink = sink;
+    p.keep_first = (window > 0 && keep_first > 0) ? keep_first : 0; p.slopes = slopes;
     // Sharing query tiles needs scratch for every (segment, head, query tile); with less than that, fewer parts.
     if (n_long_segments <= 0 || n_long_segments > n_segments) n_long_segments = n_segments;
     const int64_t n_qt = (max_q_len + BM - 1) / BM, tiles = int64_t(n_long_segments) * n_heads * n_qt;
@@ -686,6 +705,19 @@ IB_EXPORT int ib_attention_prefill_tc_biased(const void* q, const void* k_cache,
     return prefill_tc(q, k_cache, v_cache, out, block_table, max_blocks, seg_start, seg_pos0, n_segments, n_tokens, n_heads, n_kv,
                       head_dim, page_size, window, scale, n_pages, max_q_len, status, stream, split, workspace, workspace_floats,
                       counters, n_counters, n_long_segments, bias, bias_len, sink);
+}
+
+// The same with, beside bias and sink, kept first keys (with a window: every query also sees the keys below keep_first)
+// and a slope per head, float [heads]: slopes[h] * (query position - key position) is taken off the scaled score.
+IB_EXPORT int ib_attention_prefill_tc_kept(const void* q, const void* k_cache, const void* v_cache, void* out, const int* block_table,
+                                           int max_blocks, const int* seg_start, const int* seg_pos0, int n_segments, int64_t n_tokens,
+                                           int n_heads, int n_kv, int head_dim, int page_size, int window, float scale, int64_t n_pages,
+                                           int max_q_len, int* status, cudaStream_t stream, int split, float* workspace,
+                                           int64_t workspace_floats, unsigned int* counters, int64_t n_counters, int n_long_segments,
+                                           const float* bias, int bias_len, const float* sink, int keep_first, const float* slopes) {
+    return prefill_tc(q, k_cache, v_cache, out, block_table, max_blocks, seg_start, seg_pos0, n_segments, n_tokens, n_heads, n_kv,
+                      head_dim, page_size, window, scale, n_pages, max_q_len, status, stream, split, workspace, workspace_floats,
+                      counters, n_counters, n_long_segments, bias, bias_len, sink, keep_first, slopes);
 }
 
 #ifdef IB_ATTN_TRACE

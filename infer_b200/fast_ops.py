@@ -329,10 +329,12 @@ def attention_fast(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor
 
 
 def attention_prefill_biased(q, k_cache, v_cache, block_table, step, n_heads, n_kv, head_dim, window, scale,
-                             bias_by_head: Optional[torch.Tensor], sink: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
-    """The tcgen05 prefill kernel with a bias per (head, distance) (float32 [heads, L], already divided by the scale)
-    and a sink per head, on the segments of two or more tokens; the rows of one-token segments are left unwritten.
-    None if the shape is refused."""
+                             bias_by_head: Optional[torch.Tensor], sink: Optional[torch.Tensor], keep_first: int = 0,
+                             slopes: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
+    """The tcgen05 prefill kernel with a bias per (head, distance) (float32 [heads, L], already divided by the scale),
+    a sink per head, kept first keys (with a window: every query also sees the keys below ``keep_first``) and a slope
+    per head (float32 [heads]: slope * distance is taken off the scaled score), on the segments of two or more tokens;
+    the rows of one-token segments are left unwritten. None if the shape is refused."""
     n_pages, ckv, page_size, chd = k_cache.shape
     if (q.dtype != torch.bfloat16 or not ATTENTION_TC or head_dim not in ATTENTION_TC_HEAD_DIMS or page_size != 16
             or not attention_supported(n_heads, n_kv, head_dim, page_size) or not scale > 0):
@@ -347,6 +349,8 @@ def attention_prefill_biased(q, k_cache, v_cache, block_table, step, n_heads, n_
             raise KernelError(f"bias_by_head must be [{n_heads}, distances], got {tuple(bias_by_head.shape)}")
     if sink is not None:
         _check(sink, "sink", torch.float32, (n_heads,))
+    if slopes is not None:
+        _check(slopes, "slopes", torch.float32, (n_heads,))
     S = step.seg_pos0.numel()
     st = device_state(q.device)
     n_prefill = sum(1 for n in step.seg_lens if n > 1)
@@ -356,14 +360,18 @@ def attention_prefill_biased(q, k_cache, v_cache, block_table, step, n_heads, n_
         tiles = max(1, n_prefill) * n_heads * -(-step.max_q_len // 128)
         tc_ws, tc_cnt = st.workspace(tiles * split * (128 * head_dim + 256)), st.counters(tiles)
     out = torch.empty_like(q)
-    g = _fn("attn_tc", "ib_attention_prefill_tc_biased", [c_void_p] * 5 + [c_int] + [c_void_p] * 2 + [c_int, c_int64] + [c_int] * 5 +
-            [c_float, c_int64, c_int] + [c_void_p] * 2 + [c_int, c_void_p, c_int64, c_void_p, c_int64, c_int, c_void_p, c_int, c_void_p],
+    keep_first = int(keep_first or 0) if window else 0
+    kept = keep_first > 0 or slopes is not None                 # (the entry point that takes them; the other is unchanged)
+    sig = [c_void_p] * 5 + [c_int] + [c_void_p] * 2 + [c_int, c_int64] + [c_int] * 5 + [c_float, c_int64, c_int] + [c_void_p] * 2 + \
+          [c_int, c_void_p, c_int64, c_void_p, c_int64, c_int, c_void_p, c_int, c_void_p]
+    g = _fn("attn_tc", "ib_attention_prefill_tc_kept" if kept else "ib_attention_prefill_tc_biased", sig + ([c_int, c_void_p] if kept else []),
             {"IB_HEAD_DIM": head_dim})
-    _call(g, q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(), block_table.data_ptr(), block_table.shape[1],
-          step.seg_start.data_ptr(), step.seg_pos0.data_ptr(), S, T, n_heads, n_kv, head_dim, page_size, int(window or 0), float(scale),
-          n_pages, int(step.max_q_len), st.status.data_ptr(), _stream(), int(split), _ptr(tc_ws), 0 if tc_ws is None else tc_ws.numel(),
-          _ptr(tc_cnt), 0 if tc_cnt is None else tc_cnt.numel(), int(n_prefill), _ptr(bias_by_head),
-          0 if bias_by_head is None else bias_by_head.shape[1], _ptr(sink))
+    args = [q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(), block_table.data_ptr(), block_table.shape[1],
+            step.seg_start.data_ptr(), step.seg_pos0.data_ptr(), S, T, n_heads, n_kv, head_dim, page_size, int(window or 0), float(scale),
+            n_pages, int(step.max_q_len), st.status.data_ptr(), _stream(), int(split), _ptr(tc_ws), 0 if tc_ws is None else tc_ws.numel(),
+            _ptr(tc_cnt), 0 if tc_cnt is None else tc_cnt.numel(), int(n_prefill), _ptr(bias_by_head),
+            0 if bias_by_head is None else bias_by_head.shape[1], _ptr(sink)]
+    _call(g, *(args + ([keep_first, _ptr(slopes)] if kept else [])))
     return out
 
 

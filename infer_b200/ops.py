@@ -641,9 +641,7 @@ def attention_window(q, k_cache, v_cache, block_table, step, n_heads, n_kv, head
     the tensor-core kernel (bfloat16, keys and values of one size that the kernel is built for), one-token segments
     on the kernel that splits a token's keys over CTAs, into the same rows. None where a shape is refused (the caller
     then uses the plain kernel for everything). ``dist_bias_by_head``: float32 [heads, L], the bias divided by the
-    scale. ``keep_first`` and ``slopes`` as in attention_split; the tensor-core kernel keeps no first keys (prompt
-    portions of such a layer go to the caller's plain kernel, its single tokens stay here) and takes slopes as the table
-    ``dist_bias_by_head`` (row h: -slope_h * distance / scale)."""
+    scale. ``keep_first`` and ``slopes`` as in attention_split; both kernels take them."""
     from . import fast_ops
     if n_heads // n_kv > ATTENTION_SPLIT_GROUP_MAX:
         return None
@@ -651,15 +649,15 @@ def attention_window(q, k_cache, v_cache, block_table, step, n_heads, n_kv, head
     if step.max_q_len <= 1:
         return attention_split(q, k_cache, v_cache, block_table, step, n_heads, n_kv, head_dim, v_head_dim, window, scale, dist_bias, sink,
                                keep_first=keep_first, slopes=slopes)
-    if v_head_dim != head_dim or keep_first or ((dist_bias is not None or slopes is not None) and dist_bias_by_head is None):
+    if v_head_dim != head_dim or (dist_bias is not None and dist_bias_by_head is None):
         return None
     out = fast_ops.attention_prefill_biased(q, k_cache, v_cache, block_table, step, n_heads, n_kv, head_dim, window, scale,
-                                            dist_bias_by_head, sink)
+                                            dist_bias_by_head, sink, keep_first, slopes)
     if out is None:
         return None
     if any(n == 1 for n in step.seg_lens):
         attention_split(q, k_cache, v_cache, block_table, step, n_heads, n_kv, head_dim, v_head_dim, window, scale, dist_bias, sink,
-                        out, single_only=True, slopes=slopes)
+                        out, single_only=True, keep_first=keep_first, slopes=slopes)
     return out
 
 

@@ -242,12 +242,6 @@ class Attention(Mixer):
             self.q_norm_w, self.k_norm_w = params[n["q_norm"]].to(**f32).contiguous(), params[n["k_norm"]].to(**f32).contiguous()
         if self.slopes is not None:
             self.slopes_w = torch.tensor(self.slopes, **f32)
-            # for the tensor-core kernel of prompt portions: a row per head of -slope * distance / scale, as long as the
-            # engine's longest sequence (it is added to the raw score); left out where it would be large
-            L = int(self.rt.max_seq_len or 0)
-            if self.rt.fast("attention") and self.scale > 0 and self.v_dim == self.head_dim and 0 < L * self.n_heads <= (1 << 24):
-                dist = torch.arange(L, dtype=torch.float64)
-                self.bias_by_head = (-torch.tensor(self.slopes, dtype=torch.float64)[:, None] * dist[None, :] / self.scale).to(**f32).contiguous()
         if self.row_norm:
             self.q_norm_w, self.k_norm_w = params[n["q_norm"]].to(**f32).contiguous(), params[n["k_norm"]].to(**f32).contiguous()
         if self.distance_bias is not None:
@@ -324,7 +318,7 @@ class Attention(Mixer):
         ctx = None
         if self.rt.fast("attention"):
             ctx = ops.attention_window(q, cache.k, cache.v, table, step, self.n_heads, self.n_kv, self.head_dim, self.v_dim,
-                                       self.window, self.scale, None, self.sink_w, self.bias_by_head, self.keep_first, self.slopes_w)
+                                       self.window, self.scale, None, self.sink_w, None, self.keep_first, self.slopes_w)
         if ctx is None:
             ctx = ops.attention_plain(q, cache.k, cache.v, table, step.token_seg, step.positions, self.n_heads, self.n_kv,
                                       self.head_dim, self.window, self.scale, step.status, self.v_dim, None, self.sink_w,

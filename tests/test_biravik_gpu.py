@@ -177,8 +177,10 @@ def test_the_design_runs_on_its_own_kernels():
                  "ib_group_norm_gate", "ib_route", "ib_glu_act", "ib_relu_sq", "ib_silu_rows"):
         assert ran.get(kind, 0) >= 2, (kind, ran)
     assert ran.get("ib_gemm_tc", 0) >= 1                     # the tensor-core product serves the prompt's matrices
-    # every decoded token's attention runs on the kernel that splits its keys over CTAs
-    assert ran.get("ib_attention_split", 0) == 4, ran
+    # keys and values of 64 and 128: the prompt's attention runs on the tensor-core kernel, with and without kept first
+    # keys and slopes, every decoded token's on the kernel that splits its keys over CTAs, none on the plain one
+    assert ran.get("ib_attention_prefill_tc_kept", 0) == 3 and ran.get("ib_attention_prefill_tc_biased", 0) == 1, ran
+    assert ran.get("ib_attention_split", 0) == 4 and "ib_attention_plain" not in ran, ran
 
 
 # ----------------------------------------------------------------------------------------------- generation, programs

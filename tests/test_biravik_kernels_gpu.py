@@ -159,32 +159,53 @@ def test_attention_with_kept_first_keys_and_slopes_plain_and_split(sizes, window
     assert int(step.status.item()) == 0
 
 
-def test_slopes_reach_the_tensor_core_kernel_as_a_table():
-    H, G, d, scale = 4, 2, 64, 0.11
-    g = torch.Generator().manual_seed(5)
-    n, first = 300, 40
-    q = torch.randn(n, H, d, generator=g).bfloat16().double()
-    k = torch.randn(n, G, d, generator=g).bfloat16().double()
-    v = torch.randn(n, G, d, generator=g).bfloat16().double()
+@pytest.mark.parametrize("window,keep", [(None, 0), (150, 40), (128, 3), (300, 200), (40, 130), (520, 1)])
+@pytest.mark.parametrize("sizes", [(4, 2, 64), (2, 1, 128)])
+def test_prompt_portions_on_the_tensor_core_kernel_with_slopes_and_kept_first_keys(sizes, window, keep):
+    """A portion of 470 tokens behind 30 cached ones (four query tiles, the last ragged) beside a single token of another
+    request; keys at the window's two edges and at the kept keys' end stand out for the portion's last rows."""
+    H, G, d = sizes
+    scale, dtype = 0.11, torch.bfloat16
+    g = torch.Generator().manual_seed(d + (window or 0) + keep)
+    n, m, first = 500, 90, 30
+    seqs = [[torch.randn(length, hh, d, generator=g).to(dtype).double() for hh in (H, G, G)] for length in (n, m)]
     sink = torch.randn(H, generator=g)
-    slopes = torch.tensor([2.0 ** (-8.0 * (h + 1) / H) for h in range(H)])
-    k[0, 0] += 3.0 * q[299, 0] / q[299, 0].norm() * math.sqrt(d)
-    k = k.bfloat16().double()
-    want = _attention(q, k, v, scale, None, 0, slopes, sink)
-    table_row = list(np.random.default_rng(2).permutation(24))[:20]
-    kc, vc = _paged([k], [v], [table_row], 24, G, d, d, torch.bfloat16)
-    table = torch.tensor([table_row + [-1] * 4], dtype=torch.int32, device=DEV)
-    step = _Step([n - first], [first], [0])
+    slopes = torch.tensor([2.0 ** (-8.0 * (h + 1) / H) for h in range(H)]) if window is None else None
+    q, k, v = seqs[0]
+
+    def stand_out(key, query, head):
+        if 0 <= key <= query:
+            k[key, head // (H // G)] += 3.0 * q[query, head] / q[query, head].norm() * math.sqrt(d)
+    for probe in (n - 1, n - 70, 300):
+        if window is not None:
+            stand_out(probe - (window - 1), probe, 0)
+            stand_out(probe - window, probe, H - 1)
+            if probe - window >= keep:
+                stand_out(keep - 1, probe, 1 % H)
+                stand_out(keep, probe, 0)
+        else:
+            stand_out(0, probe, 0)
+    seqs[0][1] = k = k.to(dtype).double()
+    want = [_attention(*sq, scale, window, keep, slopes, sink) for sq in seqs]
+    tables = [list(range(3, 35)), [40, 36, 38, 37, 41, 39]]
+    kc, vc = _paged([s_[1] for s_ in seqs], [s_[2] for s_ in seqs], tables, 44, G, d, d, dtype)
+    table = torch.full((2, 32), -1, dtype=torch.int32)
+    for i, t in enumerate(tables):
+        table[i, :len(t)] = torch.tensor(t, dtype=torch.int32)
+    step = _Step([n - first, 1], [first, m - 1], [0, 1])
     step.seg_lens, step.seg_pos0 = step.lens, torch.tensor(step.pos0, dtype=torch.int32, device=DEV)
     step.max_q_len, step.max_ctx_len = n - first, n
-    rows = q[first:].reshape(-1, H * d).bfloat16().to(DEV).contiguous()
-    by_head = (-slopes.double()[:, None] * torch.arange(512, dtype=F)[None, :] / scale).float().to(DEV).contiguous()
-    before = ops.LAUNCH_KINDS["ib_attention_prefill_tc_biased"]
-    out = ops.attention_window(rows, kc.to(DEV), vc.to(DEV), table, step, H, G, d, d, None, scale, None, sink.to(DEV), by_head, 0, slopes.to(DEV))
-    assert out is not None and ops.LAUNCH_KINDS["ib_attention_prefill_tc_biased"] == before + 1
-    assert torch.allclose(out.double().cpu().view(-1, H, d), want[first:], rtol=3e-2, atol=3e-2)
-    # kept first keys are not the tensor-core kernel's: the caller's plain kernel serves such a portion
-    assert ops.attention_window(rows, kc.to(DEV), vc.to(DEV), table, step, H, G, d, d, 50, scale, None, sink.to(DEV), None, 8, None) is None
+    rows = torch.cat([q[first:].reshape(n - first, H * d), seqs[1][0][m - 1:].reshape(1, H * d)]).to(dtype).to(DEV).contiguous()
+    before = dict(ops.LAUNCH_KINDS)
+    out = ops.attention_window(rows, kc.to(DEV), vc.to(DEV), table.to(DEV), step, H, G, d, d, window, scale, None, sink.to(DEV), None, keep,
+                               slopes.to(DEV) if slopes is not None else None)
+    assert out is not None and ops.LAUNCH_KINDS["ib_attention_prefill_tc_kept"] == before.get("ib_attention_prefill_tc_kept", 0) + 1
+    assert ops.LAUNCH_KINDS["ib_attention_split"] == before.get("ib_attention_split", 0) + 1        # the single token beside it
+    assert int(step.status.item()) == 0
+    got = out.double().cpu().view(-1, H, d)
+    ref = torch.cat([want[0][first:], want[1][m - 1:]])
+    assert torch.allclose(got, ref, rtol=3e-2, atol=3e-2)
+    assert float((got - ref).pow(2).mean().sqrt()) < 4e-3
 
 
 # a key size below, at and above each number of state rows a lane keeps; value sizes that are no multiple of four
@@ -223,11 +244,9 @@ def test_constant_decay_scan_over_steps(sizes):
     assert bool(torch.isnan(state[1]).all())                                   # the slot nobody holds stayed untouched
 
 
-@pytest.mark.parametrize("sizes", SCAN_SIZES)
+@pytest.mark.parametrize("sizes", [(2, 16, 16), (3, 5, 5), (2, 128, 128), (1, 40, 40), (4, 64, 64), (1, 33, 33)])
 def test_scan_with_a_bonus_over_steps_from_planes(sizes):
     H, d, dv = sizes
-    if d != dv:
-        pytest.skip("planes of one width")
     seqs = _scan_case(H, d, dv, 3 * d + dv)
     g = torch.Generator().manual_seed(1)
     u = torch.randn(H, d, generator=g)
