@@ -532,12 +532,14 @@ split_attention_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, c
     }
 }
 
-// One warp per (token, head): the chunks' parts in ascending order, the sink, the division.
+// One warp per (token, head): the chunks' parts in ascending order, the sink, the division; optionally times
+// sigmoid(gate[t, gate_col + h dv + c]) (the logits of a gate per output channel, rows of leading dimension ldg).
 template <typename T>
 __global__ void split_attention_merge_kernel(const float* __restrict__ parts, const int* __restrict__ token_seg,
                                              const int* __restrict__ positions, const int* __restrict__ single_only,
                                              const float* __restrict__ sink, T* __restrict__ out, int64_t n_rows, int n_heads,
-                                             int dv, int window, int n_chunks, int keep_first) {
+                                             int dv, int window, int n_chunks, int keep_first, const T* __restrict__ gate,
+                                             int64_t ldg, int64_t gate_col) {
     ib::pdl_wait();
     const int lane = threadIdx.x & 31;
     const int64_t r = int64_t(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -551,15 +553,42 @@ __global__ void split_attention_merge_kernel(const float* __restrict__ parts, co
     const int nk = min((min(keep_first, lo) + KC - 1) / KC, lo / KC);
     const int n = min(n_chunks, nk + pos / KC - lo / KC + 1);
     const float* mine = parts + r * n_chunks * int64_t(dv + 2);
+    const int64_t stride = dv + 2;
+    // maxima and sums: a lane per chunk (in rounds of 32), then across the warp; every chunk's weight is computed once
     float m = sink ? sink[h] : -INFINITY;
-    for (int i = 0; i < n; i++) m = fmaxf(m, mine[i * int64_t(dv + 2)]);
-    float l = sink ? expf(sink[h] - m) : 0.0f;
-    for (int i = 0; i < n; i++) l += mine[i * int64_t(dv + 2) + 1] * expf(mine[i * int64_t(dv + 2)] - m);
+    for (int i = lane; i < n; i += 32) m = fmaxf(m, mine[i * stride]);
+    m = ib::warp_max(m);
+    float l = 0.0f;
+    for (int i = lane; i < n; i += 32) l += mine[i * stride + 1] * expf(mine[i * stride] - m);
+    l = ib::warp_sum(l) + (sink ? expf(sink[h] - m) : 0.0f);
     const float inv = l > 0.0f ? 1.0f / l : 0.0f;
-    for (int c = lane; c < dv; c += 32) {
-        float o = 0.0f;
-        for (int i = 0; i < n; i++) o = fmaf(mine[i * int64_t(dv + 2) + 2 + c], expf(mine[i * int64_t(dv + 2)] - m), o);
-        out[r * dv + c] = ib::from_f32<T>(o * inv);
+    float acc[8];                                            // up to 256 channels a pass (8 per lane), chunks in ascending order
+    for (int c0 = 0; c0 < dv; c0 += 256) {
+#pragma unroll
+        for (int e = 0; e < 8; e++) acc[e] = 0.0f;
+        for (int i0 = 0; i0 < n; i0 += 32) {
+            const float w_mine = i0 + lane < n ? expf(mine[(i0 + lane) * stride] - m) : 0.0f;
+            const int ni = min(32, n - i0);
+            for (int i = 0; i < ni; i++) {
+                const float w = __shfl_sync(0xffffffffu, w_mine, i);
+                const float* row = mine + (i0 + i) * stride + 2 + c0;
+#pragma unroll
+                for (int e = 0; e < 8; e++) {
+                    const int c = c0 + e * 32 + lane;
+                    if (c < dv) acc[e] = fmaf(row[e * 32 + lane], w, acc[e]);
+                }
+            }
+        }
+#pragma unroll
+        for (int e = 0; e < 8; e++) {
+            const int c = c0 + e * 32 + lane;
+            if (c >= dv) continue;
+            const float o = acc[e];
+        float y = o * inv;
+        // (a gate per output channel: the result is rounded as the ungated kernel leaves it, then multiplied)
+        if (gate) y = ib::to_f32(ib::from_f32<T>(y)) * sigmoid_(ib::to_f32(gate[t * ldg + gate_col + int64_t(h) * dv + c]));
+        out[r * dv + c] = ib::from_f32<T>(y);
+        }
     }
 }
 
@@ -864,7 +893,7 @@ state_scan_kernel(const float* __restrict__ rows, int64_t ld, int q_col, int k_c
                   const float* __restrict__ aux, int64_t lda, int aux_col, float* __restrict__ state,
                   const int* __restrict__ seg_start, const int* __restrict__ seg_slot, float* __restrict__ raw_out,
                   int n_heads, int heads_per_qk, int d, int dv, int cb, int chunk, int write_state, int pipelined,
-                  const float* __restrict__ bonus) {
+                  const float* __restrict__ bonus, int act) {
     extern __shared__ __align__(16) float sm[];
     constexpr int RP = R + 4, DPP = LK * RP;
     constexpr bool ROWS = MODE == 0 || MODE == 3;      // the decays are rows like q and k
@@ -927,8 +956,8 @@ state_scan_kernel(const float* __restrict__ rows, int64_t ld, int q_col, int k_c
             const int c = idx / d, j = idx - c * d;
             const int dst = c * DPP + (j / R) * RP + j % R;
             const float* row = rows + (t0 + c0 + c) * ld;
-            qs[dst] = row[q_col + hq * d + j];
-            ks[dst] = row[k_col + hq * d + j];
+            qs[dst] = act ? silu_(row[q_col + hq * d + j]) : row[q_col + hq * d + j];
+            ks[dst] = act ? silu_(row[k_col + hq * d + j]) : row[k_col + hq * d + j];
             if (ROWS) as[dst] = aux[(t0 + c0 + c) * lda + aux_col + h * d + j];
         }
         if (!ROWS) {
@@ -943,7 +972,8 @@ state_scan_kernel(const float* __restrict__ rows, int64_t ld, int q_col, int k_c
         }
         for (int idx = tid; idx < n * cb; idx += blockDim.x) {
             const int c = idx / cb, j = col0 + (idx - c * cb);
-            vs[idx] = j < dv ? rows[(t0 + c0 + c) * ld + v_col + h * dv + j] : 0.0f;
+            const float vv = j < dv ? rows[(t0 + c0 + c) * ld + v_col + h * dv + j] : 0.0f;
+            vs[idx] = act ? silu_(vv) : vv;
         }
     };
 
@@ -1112,7 +1142,8 @@ IB_EXPORT int ib_attention_split(const void* q, const void* k_cache, const void*
                                  const int* token_seg, const int* positions, const int* single_only, void* out, float* workspace,
                                  int64_t n_tokens, int n_heads, int n_kv, int d, int dv, int page_size, int window, float scale,
                                  int64_t n_pages, const float* dist_bias, int bias_len, const float* sink, int visible, int dtype,
-                                 int* status, cudaStream_t stream, int keep_first, const float* slopes) {
+                                 int* status, cudaStream_t stream, int keep_first, const float* slopes, const void* gate, int64_t ldg,
+                                 int64_t gate_col) {
     if (n_tokens <= 0) return IB_OK;
     if (n_kv <= 0 || n_heads % n_kv || n_heads / n_kv > GMAX)
         return ib::fail(IB_ERR_ARG, "ib_attention_split: %d heads on %d kv heads (groups of up to %d)", n_heads, n_kv, GMAX);
@@ -1145,11 +1176,11 @@ IB_EXPORT int ib_attention_split(const void* q, const void* k_cache, const void*
     if (dtype == IB_F32) {
         IB_SPLIT_BY_GROUP(float);
         IB_LAUNCH(split_attention_merge_kernel<float>, blocks_for(rows, 4), 128, 0, workspace, token_seg, positions, single_only, sink,
-                  (float*)out, rows, n_heads, dv, window, n_chunks, keep_first);
+                  (float*)out, rows, n_heads, dv, window, n_chunks, keep_first, (const float*)gate, ldg, gate_col);
     } else if (dtype == IB_BF16) {
         IB_SPLIT_BY_GROUP(bf16);
         IB_LAUNCH(split_attention_merge_kernel<bf16>, blocks_for(rows, 4), 128, 0, workspace, token_seg, positions, single_only, sink,
-                  (bf16*)out, rows, n_heads, dv, window, n_chunks, keep_first);
+                  (bf16*)out, rows, n_heads, dv, window, n_chunks, keep_first, (const bf16*)gate, ldg, gate_col);
     } else {
         return ib::fail(IB_ERR_ARG, "ib_attention_split: unknown dtype %d", dtype);
     }
@@ -1203,9 +1234,9 @@ template <int R, int MODE>
 static int launch_scan(dim3 grid, int threads, size_t smem, cudaStream_t stream, const float* rows, int64_t ld, int q_col,
                        int k_col, int v_col, const float* aux, int64_t lda, int aux_col, float* state, const int* seg_start,
                        const int* seg_slot, float* raw_out, int n_heads, int hpq, int d, int dv, int cb, int chunk, int write_state,
-                       int pipelined, const float* bonus) {
+                       int pipelined, const float* bonus, int act) {
     IB_LAUNCH((state_scan_kernel<R, MODE>), grid, threads, smem, rows, ld, q_col, k_col, v_col, aux, lda, aux_col, state, seg_start,
-              seg_slot, raw_out, n_heads, hpq, d, dv, cb, chunk, write_state, pipelined, bonus);
+              seg_slot, raw_out, n_heads, hpq, d, dv, cb, chunk, write_state, pipelined, bonus, act);
     return ib::check_launch("ib_state_scan");
 }
 
@@ -1216,7 +1247,7 @@ static int launch_scan(dim3 grid, int threads, size_t smem, cudaStream_t stream,
 IB_EXPORT int ib_state_scan(int mode, const float* rows, int64_t ld, int q_col, int k_col, int v_col, const float* aux,
                             int64_t lda, int aux_col, float* state, const int* seg_start, const int* seg_slot,
                             float* raw_out, int n_segments, int n_heads, int heads_per_qk, int d, int dv, int write_state,
-                            int spread, int sm_count, cudaStream_t stream, const float* bonus) {
+                            int spread, int sm_count, cudaStream_t stream, const float* bonus, int act) {
     if (n_segments <= 0) return IB_OK;
     if (n_heads <= 0 || n_heads > 65535 || heads_per_qk <= 0 || n_heads % heads_per_qk || d <= 0 || dv <= 0 || d > LK * 32)
         return ib::fail(IB_ERR_ARG, "ib_state_scan: %d heads with a state of %d x %d do not fit", n_heads, d, dv);
@@ -1232,7 +1263,8 @@ IB_EXPORT int ib_state_scan(int mode, const float* rows, int64_t ld, int q_col, 
     }
     // asynchronous copies of rows as they lie need every offset and size on 16 bytes; prompt portions only (a step of
     // single tokens has nothing to copy ahead)
-    const int pipelined = spread && d % 4 == 0 && dv % 4 == 0 && cb % 4 == 0 && ld % 4 == 0 && q_col % 4 == 0 && k_col % 4 == 0 &&
+    // act 1: q, k and v are z * sigmoid(z) of what the rows hold, applied while staging (not with copies as they lie)
+    const int pipelined = !act && spread && d % 4 == 0 && dv % 4 == 0 && cb % 4 == 0 && ld % 4 == 0 && q_col % 4 == 0 && k_col % 4 == 0 &&
                           v_col % 4 == 0 && (!decay_rows || (lda % 4 == 0 && aux_col % 4 == 0 && !(uintptr_t(aux) & 15))) &&
                           !(uintptr_t(rows) & 15);
     const int dpp = LK * (r + 4), n_buf = pipelined ? 2 : 1;
@@ -1245,7 +1277,7 @@ IB_EXPORT int ib_state_scan(int mode, const float* rows, int64_t ld, int q_col, 
     const int threads = cb * LK;
 #define IB_SCAN(RR, MM)                                                                                                          \
     return launch_scan<RR, MM>(grid, threads, smem, stream, rows, ld, q_col, k_col, v_col, aux, lda, aux_col, state, seg_start, \
-                               seg_slot, raw_out, n_heads, heads_per_qk, d, dv, cb, chunk, write_state, pipelined, bonus)
+                               seg_slot, raw_out, n_heads, heads_per_qk, d, dv, cb, chunk, write_state, pipelined, bonus, act)
     if (mode == 2) {
         if (r == 4) IB_SCAN(4, 2);
         if (r == 8) IB_SCAN(8, 2);

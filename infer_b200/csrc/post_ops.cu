@@ -235,6 +235,84 @@ __global__ void relu_sq_kernel(const T* __restrict__ rows, int64_t ld, int64_t c
     out[i] = ib::from_f32<T>(v * v);
 }
 
+// The same for bfloat16 rows whose sizes and addresses allow 16-byte accesses: eight columns a thread.
+__global__ void relu_sq_vec_kernel(const bf16* __restrict__ rows, int64_t ld, int64_t col0, int64_t width8, bf16* __restrict__ out, int64_t n8) {
+    ib::pdl_wait();
+    const int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i >= n8) return;
+    const int64_t t = i / width8, c = (i - t * width8) * 8;
+    const uint4 in = *reinterpret_cast<const uint4*>(rows + t * ld + col0 + c);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&in);
+    uint4 res;
+    __nv_bfloat162* rh = reinterpret_cast<__nv_bfloat162*>(&res);
+#pragma unroll
+    for (int k = 0; k < 4; k++) {
+        const float2 f = __bfloat1622float2(h[k]);
+        const float a = fmaxf(f.x, 0.0f), b = fmaxf(f.y, 0.0f);
+        rh[k] = __floats2bfloat162_rn(a * a, b * b);
+    }
+    *reinterpret_cast<uint4*>(out + i * 8) = res;
+}
+
+// group_norm_gate with one CTA per (token, group), for groups of many channels (all heads of a token at once): the
+// same result as the warp form up to the order of the sum of squares; which form runs depends on the group's size only.
+template <typename TG, typename TOut>
+__global__ void __launch_bounds__(256)
+group_norm_gate_wide_kernel(const float* __restrict__ o, const float* __restrict__ w, float eps, const TG* __restrict__ gate,
+                            int64_t ldg, int64_t gate_col, int act, TOut* __restrict__ out, int n_groups, int size) {
+    ib::pdl_wait();
+    __shared__ float red[32];
+    const int64_t r = blockIdx.x;
+    const int64_t t = r / n_groups;
+    const int g = int(r - t * n_groups);
+    const float* x = o + r * size;
+    float ss = 0.0f;
+    for (int j = threadIdx.x; j < size; j += blockDim.x) ss = fmaf(x[j], x[j], ss);
+    ss = ib::block_sum(ss, red);
+    const float f = 1.0f / sqrtf(ss / float(size) + eps);
+    for (int j = threadIdx.x; j < size; j += blockDim.x) {
+        float y = x[j] * f;
+        if (w) y *= w[int64_t(g) * size + j];
+        if (gate) {
+            const float z = ib::to_f32(gate[t * ldg + gate_col + int64_t(g) * size + j]);
+            y *= act == 1 ? silu_(z) : (act == 2 ? sigmoid_(z) : z);
+        }
+        out[r * size + j] = ib::from_f32<TOut>(y);
+    }
+}
+
+// double_exp_decay for TT tokens a CTA: a thread keeps one channel's column of `up` in flight once for all of them.
+constexpr int DECAY_TOKENS = 8;
+template <typename T>
+__global__ void __launch_bounds__(256)
+double_exp_decay_tokens_kernel(const T* __restrict__ rows, int64_t ld, int low_col, int rank, const float* __restrict__ up,
+                               const float* __restrict__ bias, float* __restrict__ decay, int channels, int64_t n_tokens) {
+    ib::pdl_wait();
+    extern __shared__ float low[];                          // [DECAY_TOKENS][rank]
+    const int64_t t0 = int64_t(blockIdx.y) * DECAY_TOKENS;
+    const int nt = int(min(int64_t(DECAY_TOKENS), n_tokens - t0));
+    for (int i = threadIdx.x; i < nt * rank; i += blockDim.x) {
+        const int tt = i / rank, r = i - tt * rank;
+        low[i] = tanhf(ib::to_f32(rows[(t0 + tt) * ld + low_col + r]));
+    }
+    __syncthreads();
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= channels) return;
+    float z[DECAY_TOKENS];
+    const float b = bias ? bias[c] : 0.0f;
+#pragma unroll
+    for (int tt = 0; tt < DECAY_TOKENS; tt++) z[tt] = b;
+    for (int r = 0; r < rank; r++) {
+        const float u = up[int64_t(r) * channels + c];
+#pragma unroll
+        for (int tt = 0; tt < DECAY_TOKENS; tt++)
+            if (tt < nt) z[tt] = fmaf(u, low[tt * rank + r], z[tt]);
+    }
+#pragma unroll
+    for (int tt = 0; tt < DECAY_TOKENS; tt++)
+        if (tt < nt) decay[(t0 + tt) * channels + c] = expf(-expf(z[tt]));
+}
+
 }  // namespace
 
 // ================================================================================================
@@ -311,19 +389,30 @@ IB_EXPORT int ib_double_exp_decay(const void* rows, int64_t ld, int low_col, int
                                   int64_t n_tokens, int channels, int dtype, cudaStream_t stream) {
     if (n_tokens <= 0 || channels <= 0) return IB_OK;
     if (rank <= 0 || rank > 8192 || n_tokens > 2147483647) return ib::fail(IB_ERR_ARG, "ib_double_exp_decay: a rank of %d", rank);
-    // tokens on the grid's y axis, in slabs of 65535
-    for (int64_t t0 = 0; t0 < n_tokens; t0 += 65535) {
-        const unsigned nt = unsigned(n_tokens - t0 < 65535 ? n_tokens - t0 : 65535);
-        const dim3 grid{blocks_for(channels, 256), nt, 1u};
+    // A few tokens (a decode step): a CTA per (token, 256 channels), so that there are CTAs enough.
+    if (n_tokens < 8 * DECAY_TOKENS) {
+        const dim3 grid1{blocks_for(channels, 256), unsigned(n_tokens), 1u};
         if (dtype == IB_F32)
-            IB_LAUNCH(double_exp_decay_kernel<float>, grid, 256, rank * sizeof(float), (const float*)rows + t0 * ld, ld, low_col, rank, up, bias,
-                      decay + t0 * channels, channels);
+            IB_LAUNCH(double_exp_decay_kernel<float>, grid1, 256, rank * sizeof(float), (const float*)rows, ld, low_col, rank, up, bias, decay, channels);
         else if (dtype == IB_BF16)
-            IB_LAUNCH(double_exp_decay_kernel<bf16>, grid, 256, rank * sizeof(float), (const bf16*)rows + t0 * ld, ld, low_col, rank, up, bias,
-                      decay + t0 * channels, channels);
+            IB_LAUNCH(double_exp_decay_kernel<bf16>, grid1, 256, rank * sizeof(float), (const bf16*)rows, ld, low_col, rank, up, bias, decay, channels);
         else
             return ib::fail(IB_ERR_ARG, "ib_double_exp_decay: unknown dtype %d", dtype);
+        return ib::check_launch("ib_double_exp_decay");
     }
+    // Otherwise groups of DECAY_TOKENS tokens on the grid's y axis. Each channel's sum runs over the rank in ascending
+    // order whatever the grouping: a token's bits do not depend on its neighbours or on which form ran.
+    const int64_t groups = (n_tokens + DECAY_TOKENS - 1) / DECAY_TOKENS;
+    if (groups > 65535 || size_t(DECAY_TOKENS) * rank * sizeof(float) > 48 * 1024)
+        return ib::fail(IB_ERR_ARG, "ib_double_exp_decay: %lld tokens at rank %d", (long long)n_tokens, rank);
+    const dim3 grid{blocks_for(channels, 256), unsigned(groups), 1u};
+    const size_t smem = size_t(DECAY_TOKENS) * rank * sizeof(float);
+    if (dtype == IB_F32)
+        IB_LAUNCH(double_exp_decay_tokens_kernel<float>, grid, 256, smem, (const float*)rows, ld, low_col, rank, up, bias, decay, channels, n_tokens);
+    else if (dtype == IB_BF16)
+        IB_LAUNCH(double_exp_decay_tokens_kernel<bf16>, grid, 256, smem, (const bf16*)rows, ld, low_col, rank, up, bias, decay, channels, n_tokens);
+    else
+        return ib::fail(IB_ERR_ARG, "ib_double_exp_decay: unknown dtype %d", dtype);
     return ib::check_launch("ib_double_exp_decay");
 }
 
@@ -332,8 +421,13 @@ IB_EXPORT int ib_group_norm_gate(const float* o, const float* w, float eps, cons
                                  cudaStream_t stream) {
     const int64_t rows = n_tokens * n_groups;
     if (rows <= 0 || size <= 0) return IB_OK;
-    const unsigned grid = blocks_for(rows, 8);
-#define IB_GN(TG, TO) IB_LAUNCH((group_norm_gate_kernel<TG, TO>), grid, 256, 0, o, w, eps, (const TG*)gate, ldg, gate_col, act, (TO*)out, rows, n_groups, size)
+    const bool wide = size >= 512;                          // (by the group's size only, never by the number of rows)
+    const unsigned grid = wide ? unsigned(rows) : blocks_for(rows, 8);
+#define IB_GN(TG, TO)                                                                                                               \
+    do {                                                                                                                            \
+        if (wide) IB_LAUNCH((group_norm_gate_wide_kernel<TG, TO>), grid, 256, 0, o, w, eps, (const TG*)gate, ldg, gate_col, act, (TO*)out, n_groups, size); \
+        else IB_LAUNCH((group_norm_gate_kernel<TG, TO>), grid, 256, 0, o, w, eps, (const TG*)gate, ldg, gate_col, act, (TO*)out, rows, n_groups, size);     \
+    } while (0)
     if (!gate || gate_dtype == IB_F32) {
         if (out_dtype == IB_F32) IB_GN(float, float);
         else if (out_dtype == IB_BF16) IB_GN(float, bf16);
@@ -354,6 +448,9 @@ IB_EXPORT int ib_relu_sq(const void* rows, int64_t ld, int64_t col0, int64_t wid
     const int64_t n = n_tokens * width;
     if (n <= 0) return IB_OK;
     if (dtype == IB_F32) IB_LAUNCH(relu_sq_kernel<float>, blocks_for(n, 256), 256, 0, (const float*)rows, ld, col0, width, (float*)out, n);
+    else if (dtype == IB_BF16 && width % 8 == 0 && ld % 8 == 0 && col0 % 8 == 0 && !((uintptr_t(rows) | uintptr_t(out)) & 15))
+        // (chosen by sizes and addresses, never by the number of rows)
+        IB_LAUNCH(relu_sq_vec_kernel, blocks_for(n / 8, 256), 256, 0, (const bf16*)rows, ld, col0, width / 8, (bf16*)out, n / 8);
     else if (dtype == IB_BF16) IB_LAUNCH(relu_sq_kernel<bf16>, blocks_for(n, 256), 256, 0, (const bf16*)rows, ld, col0, width, (bf16*)out, n);
     else return ib::fail(IB_ERR_ARG, "ib_relu_sq: unknown dtype %d", dtype);
     return ib::check_launch("ib_relu_sq");

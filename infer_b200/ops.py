@@ -593,12 +593,14 @@ def rownorm_store(rows: torch.Tensor, col0: int, wq: Optional[torch.Tensor], wk:
 
 
 def attention_split(q, k_cache, v_cache, block_table, step, n_heads, n_kv, head_dim, v_head_dim, window, scale,
-                    dist_bias=None, sink=None, out=None, single_only=False, keep_first=0, slopes=None):
+                    dist_bias=None, sink=None, out=None, single_only=False, keep_first=0, slopes=None, gate=None, gate_col=0):
     """Paged attention with keys split over CTAs (chunks of 128 keys aligned to absolute positions, merged in
     ascending order), for tokens that read a few hundred keys each: decoded tokens of a windowed layer. Takes a
     distance bias float32 [L, heads] and a sink float32 [heads]. With ``single_only`` only tokens that are a segment
     of their own are computed (into ``out``, whose other rows stay). ``keep_first``: a windowed query also sees the keys
-    at positions below it; ``slopes`` float32 [heads]: slopes[h] * distance is taken off the scaled score."""
+    at positions below it; ``slopes`` float32 [heads]: slopes[h] * distance is taken off the scaled score. ``gate``
+    (rows in q's dtype, logits of a gate per output channel from column ``gate_col``): the result is multiplied by their
+    sigmoid in the merge."""
     _check(q, "q")
     T = q.shape[0]
     n_pages, ckv, page_size, chd = k_cache.shape
@@ -620,15 +622,19 @@ def attention_split(q, k_cache, v_cache, block_table, step, n_heads, n_kv, head_
     keep_first = int(keep_first or 0) if window else 0
     if slopes is not None:
         _check(slopes, "slopes", torch.float32, (n_heads,))
+    if gate is not None:
+        _check(gate, "gate", q.dtype)
+        if gate.shape[0] != T or gate_col < 0 or gate_col + n_heads * v_head_dim > gate.shape[1]:
+            raise KernelError("the gate columns lie outside the rows")
     n_ws = int(_fn("mix", "ib_attention_split_workspace", [c_int64, c_int, c_int, c_int, c_int], restype=c_int64)(T, n_heads, v_head_dim, visible, keep_first))
     ws = torch.empty(n_ws, dtype=torch.float32, device=q.device)
     f = _fn("mix", "ib_attention_split", [c_void_p] * 4 + [c_int64] + [c_void_p] * 5 + [c_int64] + [c_int] * 6 + [c_float, c_int64,
-                                          c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p])
+                                          c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int64, c_int64])
     _call(f, q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), block_table.data_ptr(), block_table.shape[1],
           step.token_seg.data_ptr(), step.positions.data_ptr(), step.seg_start.data_ptr() if single_only else None, out.data_ptr(),
           ws.data_ptr(), T, n_heads, n_kv, head_dim, v_head_dim, page_size, int(window or 0), float(scale), n_pages,
           _ptr(dist_bias), 0 if dist_bias is None else dist_bias.shape[0], _ptr(sink), visible, dtype_code(q.dtype),
-          _ptr(step.status), _stream(), keep_first, _ptr(slopes))
+          _ptr(step.status), _stream(), keep_first, _ptr(slopes), _ptr(gate), 0 if gate is None else gate.shape[1], int(gate_col))
     return out
 
 
@@ -742,7 +748,8 @@ SCAN_SPREAD_FROM = 8          # segments of more tokens than this spread a head'
 
 def state_scan(mode: int, rows: torch.Tensor, q_col: int, k_col: int, v_col: int, aux: torch.Tensor, aux_col: int,
                state: torch.Tensor, seg_start: torch.Tensor, seg_slot: torch.Tensor, n_heads: int, heads_per_qk: int,
-               dim: int, v_dim: int, write_state: bool = True, max_len: int = 1, bonus: Optional[torch.Tensor] = None) -> torch.Tensor:
+               dim: int, v_dim: int, write_state: bool = True, max_len: int = 1, bonus: Optional[torch.Tensor] = None,
+               silu: bool = False) -> torch.Tensor:
     """A linear recurrence with a float32 matrix state [slots, heads, dim, v_dim], over the tokens of every segment
     in order. SCAN_ROW_DECAY: S <- diag(a) S + k v^T, o = S^T q, with a in ``aux`` columns aux_col + h * dim.
     SCAN_DELTA_RULE: S <- g S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q, with ``aux`` columns [g (heads) | beta
@@ -750,6 +757,7 @@ def state_scan(mode: int, rows: torch.Tensor, q_col: int, k_col: int, v_col: int
     v_col + h * v_dim of the float32 ``rows``. SCAN_HEAD_DECAY: S <- g_h S + k v^T, o = S^T q, with ``aux`` float32
     [heads] (a constant per head) or [T, ...] with g at column aux_col + h. SCAN_BONUS: o = (S + diag(u) k v^T)^T q, then
     S <- diag(a) S + k v^T, with a as for SCAN_ROW_DECAY and u = ``bonus`` float32 [heads, dim].
+    ``silu``: q, k and v are z * sigmoid(z) of what the rows hold (applied while the tokens are staged).
     Returns o float32 [T, heads * v_dim]."""
     _check(rows, "rows", torch.float32)
     _check(aux, "aux", torch.float32)
@@ -792,10 +800,10 @@ def state_scan(mode: int, rows: torch.Tensor, q_col: int, k_col: int, v_col: int
     spread = int(max_len) >= SCAN_SPREAD_FROM
     sm_count = torch.cuda.get_device_properties(rows.device).multi_processor_count if spread else 0
     f = _fn("mix", "ib_state_scan", [c_int, c_void_p, c_int64, c_int, c_int, c_int, c_void_p, c_int64, c_int, c_void_p, c_void_p,
-                                     c_void_p, c_void_p] + [c_int] * 8 + [c_void_p, c_void_p])
+                                     c_void_p, c_void_p] + [c_int] * 8 + [c_void_p, c_void_p, c_int])
     _call(f, int(mode), rows.data_ptr(), ld, int(q_col), int(k_col), int(v_col), aux.data_ptr(), lda, int(aux_col),
           state.data_ptr(), seg_start.data_ptr(), seg_slot.data_ptr(), out.data_ptr(), S, n_heads, int(heads_per_qk), dim, v_dim,
-          int(write_state), int(spread), sm_count, _stream(), _ptr(bonus) if mode == SCAN_BONUS else None)
+          int(write_state), int(spread), sm_count, _stream(), _ptr(bonus) if mode == SCAN_BONUS else None, int(bool(silu)))
     return out
 
 

@@ -316,6 +316,12 @@ class Attention(Mixer):
                              self.values_are_keys, step, table, cache.k, cache.v, self.n_heads, self.n_kv, self.head_dim, self.v_dim,
                              write_cache)
         ctx = None
+        if self.rt.fast("attention") and step.max_q_len <= 1 and self.n_heads // self.n_kv <= ops.ATTENTION_SPLIT_GROUP_MAX:
+            # single tokens only: the kernel that merges a token's key chunks also applies the gate
+            ctx = ops.attention_split(q, cache.k, cache.v, table, step, self.n_heads, self.n_kv, self.head_dim, self.v_dim, self.window,
+                                      self.scale, None, self.sink_w, keep_first=self.keep_first, slopes=self.slopes_w,
+                                      gate=qkv if self.channel_gate else None, gate_col=col0 + self.n_qkv)
+            return self._project_out(ctx, residual)
         if self.rt.fast("attention"):
             ctx = ops.attention_window(q, cache.k, cache.v, table, step, self.n_heads, self.n_kv, self.head_dim, self.v_dim,
                                        self.window, self.scale, None, self.sink_w, None, self.keep_first, self.slopes_w)

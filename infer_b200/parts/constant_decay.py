@@ -89,9 +89,13 @@ class ConstantDecayAttention(Mixer):
     def forward(self, x, step, cache, residual, write_cache=True):
         nq, nv = self.n_heads * self.dim, self.n_heads * self.v_dim
         rows, c0 = own_or_projected(self, x, self.proj, torch.float32)
-        ops.silu_rows(rows, c0, 2 * nq + nv)
+        # prompt portions: the activation in a pass of its own, so that the scan copies its rows as they lie, a chunk
+        # ahead; steps of a few tokens per request: inside the scan's staging (one launch less; the same arithmetic)
+        in_scan = step.max_q_len < ops.SCAN_SPREAD_FROM
+        if not in_scan:
+            ops.silu_rows(rows, c0, 2 * nq + nv)
         o = ops.state_scan(ops.SCAN_HEAD_DECAY, rows, c0, c0 + nq, c0 + 2 * nq, self.decay_w, 0, cache["S"], step.seg_start,
-                           step.seg_slot, self.n_heads, 1, self.dim, self.v_dim, write_cache, step.max_q_len)
+                           step.seg_slot, self.n_heads, 1, self.dim, self.v_dim, write_cache, step.max_q_len, silu=in_scan)
         y = ops.group_norm_gate(o, self.norm_w, self.eps, rows, c0 + 2 * nq + nv, "sigmoid", 1, nv, self.rt.dtype)
         if residual is None:
             return self.o(y, out_dtype=torch.float32)

@@ -108,11 +108,29 @@ class ShiftedDecayMixing(Mixer):
         T, C = x.shape[0], self.n_heads * self.dim
         mixes = ops.shift_mix(x, cache["last"], self.mu, step, self.rt.dtype, write_cache)          # [5, T, hidden]
         rkv = torch.empty((3, T, C), dtype=torch.float32, device=x.device)
+        # In a decode step every kernel is a few microseconds of latency: the five products read five different
+        # mixtures and write nothing in common, so two of them and the decays go to a side stream beside the other three.
+        from .block import PARALLEL_BRANCHES, _side_streams
+        side = _side_streams(x.device)[1] if (PARALLEL_BRANCHES and step.decode_only and self.rt.dtype != torch.float32) else None
+        if side is not None:
+            main = torch.cuda.current_stream(x.device)
+            fork = torch.cuda.Event()
+            fork.record(main)
+            side.wait_event(fork)
+            with torch.cuda.stream(side):
+                low = self.lin["w"](mixes[4], out_dtype=torch.float32)
+                decay = ops.double_exp_decay(low, 0, self.rank, self.up, self.up_bias)
+                gate = self.lin["g"](mixes[3])
+                done = torch.cuda.Event()
+                done.record(side)
         for i, s in enumerate(("r", "k", "v")):
             self.lin[s](mixes[i], out=rkv[i])
-        gate = self.lin["g"](mixes[3])
-        low = self.lin["w"](mixes[4], out_dtype=torch.float32)
-        decay = ops.double_exp_decay(low, 0, self.rank, self.up, self.up_bias)
+        if side is not None:
+            main.wait_event(done)
+        else:
+            gate = self.lin["g"](mixes[3])
+            low = self.lin["w"](mixes[4], out_dtype=torch.float32)
+            decay = ops.double_exp_decay(low, 0, self.rank, self.up, self.up_bias)
         o = ops.state_scan(ops.SCAN_BONUS, rkv, (0, 0), (1, 0), (2, 0), decay, 0, cache["S"], step.seg_start, step.seg_slot,
                            self.n_heads, 1, self.dim, self.dim, write_cache, step.max_q_len, bonus=self.bonus)
         y = ops.group_norm_gate(o, self.norm_w, self.eps, gate, 0, "silu", self.n_heads, self.dim, self.rt.dtype)

@@ -156,6 +156,12 @@ def test_attention_with_kept_first_keys_and_slopes_plain_and_split(sizes, window
     got = out.double().cpu().view(-1, H, dv)
     assert torch.allclose(got[:len(probes)], want[probes], **_tol(dtype))
     assert float((got[len(probes):] - 7.0).abs().sum()) == 0.0               # the longer segment's rows were left alone
+    # the merge may apply a gate per output channel: the same bits as the ungated result through the gate's own kernel
+    gate = torch.randn(rows.shape[0], 3 + H * dv, generator=g).to(dtype).to(DEV)
+    gated = torch.full((rows.shape[0], H * dv), 7.0, dtype=dtype, device=DEV)
+    ops.attention_split(rows, kc.to(DEV), vc.to(DEV), table, step, H, G, d, dv, window, scale, None, sink.to(DEV), gated, single_only=True,
+                        keep_first=keep, slopes=sl, gate=gate, gate_col=3)
+    assert torch.equal(gated[:len(probes)], ops.gate_mul(out[:len(probes)].clone(), gate[:len(probes)].contiguous(), 3))
     assert int(step.status.item()) == 0
 
 
@@ -265,6 +271,25 @@ def test_scan_with_a_bonus_over_steps_from_planes(sizes):
         assert torch.allclose(o, want, rtol=2e-5, atol=2e-5)
         for s, m in zip((0, 2), lens):
             at[s] += m
+
+
+@pytest.mark.parametrize("sizes", [(2, 16, 32), (3, 5, 9), (2, 128, 64)])
+def test_the_activation_inside_the_scan_equals_the_activation_before_it(sizes):
+    H, d, dv = sizes
+    g = torch.Generator().manual_seed(d)
+    lens = [5, 1, 3]
+    step = _Step(lens, [0, 0, 0], [0, 1, 2])
+    rows = torch.randn(sum(lens), 4 + 2 * H * d + H * dv, generator=g).to(DEV)
+    decay = torch.rand(H, generator=g).to(DEV)
+    one, two = torch.zeros((3, H, d, dv), device=DEV), torch.zeros((3, H, d, dv), device=DEV)
+    a = ops.state_scan(ops.SCAN_HEAD_DECAY, rows, 4, 4 + H * d, 4 + 2 * H * d, decay, 0, one, step.seg_start, step.seg_slot, H, 1, d, dv,
+                       True, max(lens), silu=True)
+    act = ops.silu_rows(rows.clone(), 4, 2 * H * d + H * dv)
+    for max_len in (max(lens), 64):                               # the few-token form, and the form of prompt portions
+        two.zero_()
+        b = ops.state_scan(ops.SCAN_HEAD_DECAY, act, 4, 4 + H * d, 4 + 2 * H * d, decay, 0, two, step.seg_start, step.seg_slot, H, 1, d, dv,
+                           True, max_len)
+        assert torch.equal(a, b) and torch.equal(one, two)
 
 
 def test_scans_with_unequal_key_and_value_sizes_and_bit_equal_cuttings():
