@@ -55,12 +55,12 @@ CASES: Dict[str, dict] = {
         {"type": "attention", "mixer": _att(4, 2, 16, 0.3, (24, 5), (1000.0, 8, (4.0, 64, 8.0, 1.0))), "mlp": _moe(6, 2, 24)},
         {"type": "parallel", "mixer": _par(_left(4, 2, 16, 24, 0.2, (0.5, 7)), 0.7, _right(2, 16, 32, (0.5, 0.97)), 1.2),
          "mlp": {"kind": "dense", "ff": 40}}]),
-    # nothing a multiple of eight; the parallel layer first; a window of 33 keeping 20 (across a page border), one of 5
+    # nothing a multiple of eight; the parallel layer first; a window of 33 keeping 18 (across a page border), one of 5
     # keeping none and one of 3 keeping 1; rotation without interpolation; no temperature; a layer without
     # feed-forward; a router that uses every expert and one that chooses a single one; one kv head; decays 1 and 0
     "b": _base(97, 36, 3e-6, 1.0, 1.0, [
         {"type": "parallel", "mixer": _par(_left(3, 3, 10, 7, 0.3, None), 1.0, _right(3, 5, 9, (1.0, 0.0, 0.9)), 0.5), "mlp": None},
-        {"type": "attention", "mixer": _att(3, 1, 10, 0.4, (33, 20), (50.0, 10, None)), "mlp": _moe(4, 4, 10)},
+        {"type": "attention", "mixer": _att(3, 1, 10, 0.4, (33, 18), (50.0, 10, None)), "mlp": _moe(4, 4, 10)},
         {"type": "wkv", "mixer": {"heads": 3, "dim": 5, "rank": 3}, "mlp": _moe(9, 1, 5)},
         {"type": "attention", "mixer": _att(2, 2, 6, 0.5, (5, 0), None), "mlp": {"kind": "dense", "ff": 20}},
         {"type": "attention", "mixer": _att(1, 1, 12, 0.25, (3, 1), (10000.0, 2, (2.0, 16, 4.0, 0.5))), "mlp": None},
@@ -70,7 +70,7 @@ CASES: Dict[str, dict] = {
     "c": _base(256, 128, 2e-6, 3.0, 12.0, [
         {"type": "parallel", "mixer": _par(_left(8, 2, 64, 64, 0.11, (0.3, 50)), 0.8, _right(3, 24, 40, (0.6, 0.9, 0.999)), 0.9),
          "mlp": _moe(8, 2, 32)},
-        {"type": "attention", "mixer": _att(4, 1, 64, 0.125, (150, 40), (20000.0, 64, (8.0, 256, 32.0, 1.0))), "mlp": {"kind": "dense", "ff": 256}},
+        {"type": "attention", "mixer": _att(4, 1, 64, 0.12, (150, 40), (30000.0, 64, (6.0, 256, 24.0, 1.5))), "mlp": {"kind": "dense", "ff": 256}},
         {"type": "wkv", "mixer": {"heads": 2, "dim": 128, "rank": 16}, "mlp": None},
         {"type": "attention", "mixer": _att(2, 2, 128, 0.09, None, (500.0, 32, None)), "mlp": _moe(3, 2, 64)},
         {"type": "parallel", "mixer": _par(_left(2, 2, 128, 128, 0.08, None), 1.1, _right(2, 128, 64, (0.95, 0.5)), 0.4),

@@ -147,7 +147,7 @@ def test_cache_needs_and_kept_first_pages():
     assert isinstance(needs[0], CompositeNeed) and isinstance(needs[0].parts["first"], PagedKVNeed)
     assert needs[0].parts["first"].window is None and needs[0].parts["first"].value_dim == 7
     assert needs[0].parts["second"].shapes["S"][0] == (3, 5, 9)
-    assert needs[1] == PagedKVNeed(1, 10, 33, None, keep_first=20)
+    assert needs[1] == PagedKVNeed(1, 10, 33, None, keep_first=18)
     assert isinstance(needs[2], StateNeed) and needs[2].shapes["S"][0] == (3, 5, 5) and needs[2].shapes["last"][0] == (36,)
     assert needs[3] == PagedKVNeed(2, 6, 5, None) and needs[4] == PagedKVNeed(1, 12, 3, None, keep_first=1)
     mgr = CacheManager(needs, n_pages=12, page_size=16, n_slots=2)
@@ -157,7 +157,7 @@ def test_cache_needs_and_kept_first_pages():
         assert mgr.reserve("x", 16)
         mgr.advance("x", 16)
     table = mgr.block_table("x", group)
-    # 160 positions, a window of 33 keeping 20: pages 0 and 1 hold kept keys, page 7 (positions 112..127) is the first
+    # 160 positions, a window of 33 keeping 18: pages 0 and 1 hold kept keys, page 7 (positions 112..127) is the first
     # that a later query's window can reach (160 - 33 + 1 = 128 is its first key), so 2..7 went back
     assert [p >= 0 for p in table] == [True, True] + [False] * 6 + [True, True]
     plain_group = mgr.group_of_cache[3][0]
